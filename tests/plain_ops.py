@@ -121,12 +121,90 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
+def embedding_positions(table, place_table, ids, positions, norm_weight, eps, residual, scale=1.0) -> None:
+    x = table[ids.long()].float() * np.float32(scale)
+    if place_table is not None:
+        x = x + place_table[positions.long()].float()
+    if norm_weight is not None:
+        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + np.float32(eps)) * norm_weight
+    _store(residual, x)
+
+
+def activation(kind, x, out) -> None:
+    z = x.float()
+    if kind == "relu_squared":
+        y = torch.relu(z) ** 2
+    elif kind == "gelu_tanh":
+        y = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    else:
+        y = z * torch.sigmoid(z)
+    _store(out, y)
+
+
+def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_rows) -> None:
+    width = out.shape[1]
+    rows = zxg.float()
+    z = torch.sigmoid(rows[:, :width] + bias_z)
+    u = rows[:, width : 2 * width] + bias_x
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    gate = rows[:, 2 * width :]
+    gate = gate * torch.sigmoid(gate)
+    for entry in range(state_slots.shape[0]):
+        s = state[int(state_slots[entry])].clone()
+        for t in range(int(seq_starts[entry]), int(seq_starts[entry + 1])):
+            s = (1.0 - z[t]) * s + z[t] * cand[t]
+            out[t] = (s * gate[t]).to(out.dtype)
+        state[int(state_slots[entry])] = s
+
+
+def _planes(cache):
+    if cache.pages is not None:
+        return cache.pages[:, 0], cache.pages[:, 1]
+    return cache.plane_pages
+
+
+def store_kv_planes(rows, k_offset, v_offset, positions, token_seq, cache, kv_heads, key_dim, value_dim) -> None:
+    k_pages, v_pages = _planes(cache)
+    for t in range(rows.shape[0]):
+        pos = int(positions[t])
+        page = int(cache.block_table[int(token_seq[t]), pos // cache.page_size])
+        assert page >= 0, "a token is written to a page its request does not hold"
+        k_pages[page, :, pos % cache.page_size, :] = rows[t, k_offset : k_offset + kv_heads * key_dim].view(kv_heads, key_dim)
+        v_pages[page, :, pos % cache.page_size, :] = rows[t, v_offset : v_offset + kv_heads * value_dim].view(kv_heads, value_dim)
+
+
+def mixed_heads_attention(rows, gate_offset, positions, token_seq, cache, slopes, mix, out, heads, kv_heads, key_dim, value_dim, window, scale, batch=None) -> None:
+    k_pages, v_pages = _planes(cache)
+    tokens, group, size = rows.shape[0], heads // kv_heads, cache.page_size
+    result = torch.zeros(tokens, heads * value_dim)
+    for t in range(tokens):
+        pos = int(positions[t])
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        keys = torch.arange(lo, pos + 1)
+        page_ids = cache.block_table[int(token_seq[t]), keys // size].long()
+        assert bool((page_ids >= 0).all()), "attention reads a page its request does not hold"
+        k = k_pages[page_ids, :, keys % size, :].float()       # [keys, kv heads, key_dim]
+        v = v_pages[page_ids, :, keys % size, :].float()
+        q = rows[t, : heads * key_dim].float().view(heads, key_dim)
+        raw = torch.stack([(k[:, g // group, :] @ q[g]) * np.float32(scale) for g in range(heads)])   # [heads, keys]
+        if slopes is not None:
+            raw = raw - slopes[:, None] * (pos - keys).float()[None, :]
+        if mix is not None:
+            raw = mix @ raw
+        p = torch.softmax(raw, -1)
+        mixed = torch.cat([p[h] @ v[:, h // group, :] for h in range(heads)])
+        if gate_offset >= 0:
+            mixed = mixed * torch.sigmoid(rows[t, gate_offset : gate_offset + heads * value_dim].float())
+        result[t] = mixed
+    _store(out, result)
+
+
 def can_accumulate(rows: int, weight) -> bool:
     return False   # no product adds into the residual here: the block adds the part's output in the norm that follows
 
 
 _NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample",
-          "can_accumulate"]
+          "can_accumulate", "embedding_positions", "activation", "mingru_scan", "store_kv_planes", "mixed_heads_attention"]
 
 
 def install(monkeypatch) -> None:

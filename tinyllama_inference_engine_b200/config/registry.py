@@ -1,7 +1,7 @@
 """One registry from an architecture's name to what builds its model.
 
 The reference has a single hard-wired class and only checks ``model_type == "llama"``
-(src/model_config.cpp:25).  Here config.json's ``architectures[0]`` (or its
+(src/model_config.cpp:25).  Here config.json's ``architectures[0]`` (or ``architecture``, or its
 ``model_type``) selects an ``Architecture``: the typed configuration class and the
 function that turns a configuration into a ``ModelSpec``.  Nothing else in the
 framework names a model.
@@ -42,8 +42,10 @@ def registered_architectures() -> tuple[str, ...]:
 
 
 def architecture_for(config: dict) -> Architecture:
-    """Choose by ``architectures[0]``, falling back to ``model_type``."""
+    """Choose by ``architectures[0]`` (or the single name under ``architecture``), falling back to ``model_type``."""
     names = config.get("architectures") or []
+    if isinstance(config.get("architecture"), str):
+        names = [*names, config["architecture"]]
     for name in names:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]

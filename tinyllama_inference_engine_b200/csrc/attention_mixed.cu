@@ -1,0 +1,258 @@
+// Paged attention whose heads talk to one another before the softmax, with a distance bias and an output gate: the general
+// kernel (any sizes, both storage types, 32-bit arithmetic), for prompt portions and decoded tokens alike.
+//
+// For query token t at position i of its request, key position j, query head g (key/value head g / (H / G)):
+//   raw_g(i, j)   = (q_g . k_j) * scale - slope_g * (i - j)              (slopes optional)
+//   mixed_h(i, j) = sum_g M[h, g] raw_g(i, j)                             (M optional: H x H, row h mixes into head h)
+//   visible: 0 <= i - j, and i - j < window if window > 0
+//   out_h = softmax_j(mixed_h) . v_j                                      (values of value_dim, keys of key_dim)
+//   out   = concat_h(out_h) * sigmoid(gate)                               (gate optional: H * value_dim columns of the same row)
+// The mix needs every head's score of a (query, key) pair in one place, so a CTA owns one query token with all its heads: per
+// tile of 32 keys the warps take the heads' raw scores (a lane per key), then the mixed rows with their running maximum and sum
+// (a warp per head), then every thread adds the tile into its share of the H * value_dim outputs.  Tiles start at the first
+// visible key, so the order of a row's sums depends on the row's position alone: rows are bit-identical however the step was
+// cut or batched.
+//
+// Pages: keys [page][kv head][slot][key_dim] and values [page][kv head][slot][value_dim], each with a page stride of its own
+// (two planes of one tensor when the sizes agree, two tensors when they do not).
+#include "common.cuh"
+
+namespace tlie {
+
+constexpr int kMixKeys = 32;        // keys per tile: a lane each
+constexpr int kMixThreads = 256;
+
+// k and v of the step's tokens into their pages.
+template <typename T>
+__global__ void store_kv_planes_kernel(const T* __restrict__ rows, int row_stride, int k_offset, int v_offset, const int* __restrict__ positions,
+                                       const int* __restrict__ token_seq, const int* __restrict__ block_table, int table_stride,
+                                       T* __restrict__ k_pages, long long k_page_stride, T* __restrict__ v_pages, long long v_page_stride,
+                                       int kv_heads, int key_dim, int value_dim, int page_size) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int page = block_table[(size_t)token_seq[t] * table_stride + pos / page_size];
+  if (page < 0) return;   // a position its request holds no page for is never read either
+  const int slot = pos % page_size;
+  const T* row = rows + (size_t)t * row_stride;
+  for (int i = threadIdx.x; i < kv_heads * key_dim; i += blockDim.x) {
+    const int head = i / key_dim, d = i - head * key_dim;
+    k_pages[(size_t)page * k_page_stride + ((size_t)head * page_size + slot) * key_dim + d] = row[k_offset + i];
+  }
+  for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+    const int head = i / value_dim, d = i - head * value_dim;
+    v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = row[v_offset + i];
+  }
+}
+
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const float* __restrict__ k, int n) {
+  float dot = 0.0f;
+  if ((n & 3) == 0) {
+    for (int d = 0; d < n; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(k + d);
+      dot += q[d] * kv.x;
+      dot += q[d + 1] * kv.y;
+      dot += q[d + 2] * kv.z;
+      dot += q[d + 3] * kv.w;
+    }
+  } else {
+    for (int d = 0; d < n; ++d) dot += q[d] * k[d];
+  }
+  return dot;
+}
+
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int n) {
+  float dot = 0.0f;
+  if ((n & 7) == 0) {
+    for (int d = 0; d < n; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dot += q[d + 2 * i] * __bfloat162float(pairs[i].x);
+        dot += q[d + 2 * i + 1] * __bfloat162float(pairs[i].y);
+      }
+    }
+  } else {
+    for (int d = 0; d < n; ++d) dot += q[d] * __bfloat162float(k[d]);
+  }
+  return dot;
+}
+
+template <typename T, int ACC>
+__global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
+    const T* __restrict__ rows, int row_stride, int gate_offset, const T* __restrict__ k_pages, long long k_page_stride,
+    const T* __restrict__ v_pages, long long v_page_stride, const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, const float* __restrict__ mix, T* __restrict__ out,
+    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale) {
+  extern __shared__ __align__(16) unsigned char smem_bytes[];
+  long long* k_at = reinterpret_cast<long long*>(smem_bytes);   // [32] where a key's row starts in its plane (head 0)
+  long long* v_at = k_at + kMixKeys;
+  float* q_s = reinterpret_cast<float*>(v_at + kMixKeys);   // [heads][key_dim]
+  float* mix_s = q_s + heads * key_dim;          // [heads][heads]
+  float* raw_s = mix_s + (mix ? heads * heads : 0);   // [heads][32]
+  float* p_s = raw_s + heads * kMixKeys;         // [heads][32]
+  float* max_s = p_s + heads * kMixKeys;         // [heads] running maximum
+  float* sum_s = max_s + heads;                  // [heads] running sum
+  float* rescale_s = sum_s + heads;              // [heads] what this tile shrinks the sums so far by
+
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int warps = kMixThreads / 32;
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)token_seq[t] * table_stride;
+  const T* row = rows + (size_t)t * row_stride;
+  const int group = heads / kv_heads;
+  const int outputs = heads * value_dim;
+
+  for (int i = tid; i < heads * key_dim; i += kMixThreads) q_s[i] = to_float(row[i]);
+  if (mix)
+    for (int i = tid; i < heads * heads; i += kMixThreads) mix_s[i] = mix[i];
+  for (int i = tid; i < heads; i += kMixThreads) {
+    max_s[i] = -INFINITY;
+    sum_s[i] = 0.0f;
+  }
+
+  float acc[ACC];
+  int head_of[ACC], value_at[ACC];   // the output's head, and where its element lies inside a token's value plane entry
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) {
+    const int o = tid + i * kMixThreads;
+    acc[i] = 0.0f;
+    head_of[i] = o < outputs ? o / value_dim : 0;
+    value_at[i] = (head_of[i] / group) * page_size * value_dim + (o - head_of[i] * value_dim);
+  }
+
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  for (int base = lo; base <= pos; base += kMixKeys) {
+    const int count = min(kMixKeys, pos - base + 1);
+    __syncthreads();   // the tile before is done with k_at / v_at (and, the first time, q_s and the running sums are in place)
+    if (tid < count) {
+      const int key = base + tid;
+      const long long page = table[key / page_size];
+      const int slot = key % page_size;
+      k_at[tid] = page * k_page_stride + (long long)slot * key_dim;
+      v_at[tid] = page * v_page_stride + (long long)slot * value_dim;
+    }
+    __syncthreads();
+    // raw scores: a warp per head, a lane per key
+    for (int g = warp; g < heads; g += warps) {
+      float raw = 0.0f;
+      if (lane < count) {
+        const T* k_row = k_pages + k_at[lane] + (size_t)(g / group) * page_size * key_dim;
+        raw = dot_row(q_s + g * key_dim, k_row, key_dim) * scale;
+        if (slopes) raw -= slopes[g] * (float)(pos - (base + lane));
+      }
+      raw_s[g * kMixKeys + lane] = raw;
+    }
+    __syncthreads();
+    // the heads' scores mixed, and the softmax's running maximum and sum: a warp per head
+    for (int h = warp; h < heads; h += warps) {
+      float score;
+      if (mix) {
+        score = 0.0f;
+        for (int g = 0; g < heads; ++g) score += mix_s[h * heads + g] * raw_s[g * kMixKeys + lane];
+      } else {
+        score = raw_s[h * kMixKeys + lane];
+      }
+      if (lane >= count) score = -INFINITY;
+      const float before = max_s[h];
+      const float now = fmaxf(before, warp_max(score));
+      const float shrink = expf(before - now);   // exp(-inf) = 0 on the first tile
+      const float p = lane < count ? expf(score - now) : 0.0f;
+      const float total = warp_sum(p);
+      p_s[h * kMixKeys + lane] = p;
+      __syncwarp();
+      if (lane == 0) {
+        max_s[h] = now;
+        sum_s[h] = sum_s[h] * shrink + total;
+        rescale_s[h] = shrink;
+      }
+    }
+    __syncthreads();
+    // weights times values: every thread its share of the outputs
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) acc[i] *= rescale_s[head_of[i]];
+    for (int j = 0; j < count; ++j) {
+      const T* v_row = v_pages + v_at[j];
+#pragma unroll
+      for (int i = 0; i < ACC; ++i)
+        if (tid + i * kMixThreads < outputs) acc[i] += p_s[head_of[i] * kMixKeys + j] * to_float(v_row[value_at[i]]);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) {
+    const int o = tid + i * kMixThreads;
+    if (o < outputs) {
+      float v = acc[i] / sum_s[head_of[i]];
+      if (gate_offset >= 0) {
+        const float g = to_float(row[gate_offset + o]);
+        v *= 1.0f / (1.0f + expf(-g));
+      }
+      out[(size_t)t * outputs + o] = from_float<T>(v);
+    }
+  }
+}
+
+template <typename T, int ACC>
+static int launch_mixed(const void* rows, int row_stride, int gate_offset, const void* k_pages, long long k_page_stride, const void* v_pages,
+                        long long v_page_stride, const int* positions, const int* token_seq, const int* block_table, int table_stride,
+                        const float* slopes, const float* mix, void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
+                        int page_size, int window, float scale, size_t smem, cudaStream_t stream) {
+  auto kernel = mixed_heads_attention_kernel<T, ACC>;
+  if (smem > 48 * 1024) {
+    const cudaError_t set = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (set != cudaSuccess) return (int)set;
+  }
+  kernel<<<tokens, kMixThreads, smem, stream>>>((const T*)rows, row_stride, gate_offset, (const T*)k_pages, k_page_stride, (const T*)v_pages,
+                                                v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
+                                                kv_heads, key_dim, value_dim, page_size, window, scale);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+TLIE_EXPORT int tlie_store_kv_planes(int dtype, const void* rows, int row_stride, int k_offset, int v_offset, const int* positions,
+                                     const int* token_seq, const int* block_table, int table_stride, void* k_pages, long long k_page_stride,
+                                     void* v_pages, long long v_page_stride, int tokens, int kv_heads, int key_dim, int value_dim, int page_size,
+                                     cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == TLIE_F32)
+    store_kv_planes_kernel<float><<<tokens, 128, 0, stream>>>((const float*)rows, row_stride, k_offset, v_offset, positions, token_seq, block_table,
+                                                              table_stride, (float*)k_pages, k_page_stride, (float*)v_pages, v_page_stride, kv_heads,
+                                                              key_dim, value_dim, page_size);
+  else
+    store_kv_planes_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, k_offset, v_offset, positions, token_seq,
+                                                                      block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride,
+                                                                      (__nv_bfloat16*)v_pages, v_page_stride, kv_heads, key_dim, value_dim, page_size);
+  return (int)cudaGetLastError();
+}
+
+// ``gate_offset`` < 0: no output gate.  ``slopes`` / ``mix`` null: no distance bias / heads left as they are.
+TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_stride, int gate_offset, const void* k_pages,
+                                           long long k_page_stride, const void* v_pages, long long v_page_stride, const int* positions,
+                                           const int* token_seq, const int* block_table, int table_stride, const float* slopes, const float* mix,
+                                           void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window,
+                                           float scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0) return (int)cudaErrorInvalidValue;
+  const int outputs = heads * value_dim;
+  if (outputs > 32 * kMixThreads) return (int)cudaErrorInvalidValue;
+  const size_t floats = (size_t)heads * key_dim + (mix ? (size_t)heads * heads : 0) + 2 * (size_t)heads * kMixKeys + 3 * (size_t)heads;
+  const size_t smem = floats * sizeof(float) + 2 * kMixKeys * sizeof(long long);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define TLIE_MIXED(T, ACC)                                                                                                                    \
+  return launch_mixed<T, ACC>(rows, row_stride, gate_offset, k_pages, k_page_stride, v_pages, v_page_stride, positions, token_seq, block_table, \
+                              table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, stream)
+  if (dtype == TLIE_F32) {
+    if (outputs <= 4 * kMixThreads) TLIE_MIXED(float, 4);
+    if (outputs <= 16 * kMixThreads) TLIE_MIXED(float, 16);
+    TLIE_MIXED(float, 32);
+  }
+  if (outputs <= 4 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 4);
+  if (outputs <= 16 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 16);
+  TLIE_MIXED(__nv_bfloat16, 32);
+#undef TLIE_MIXED
+}

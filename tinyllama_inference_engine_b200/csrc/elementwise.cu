@@ -220,6 +220,70 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+
+// residual[t, :] = norm(float(table[ids[t], :]) * scale + float(place_table[positions[t], :])) : the embedding of models that add a
+// learned vector per position and normalise the sum before the first layer.  ``place_table`` and ``norm_weight`` may each be
+// null (no position vector; no norm).  The sum, the statistics and the result are 32-bit.  A position beyond the table reads
+// its last row and sets bit 2 of the error word; a token id outside the table is treated as in embedding_kernel.
+template <typename T>
+__global__ void embedding_positions_kernel(const T* __restrict__ table, const T* __restrict__ place_table, const int* __restrict__ ids,
+                                           const int* __restrict__ positions, const float* __restrict__ norm_weight, float eps, float scale,
+                                           float* __restrict__ residual, int hidden, int vocab, int places, int* __restrict__ error_flag) {
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && error_flag != nullptr) atomicOr(error_flag, 2);
+    id = 0;
+  }
+  const T* src = table + (size_t)id * hidden;
+  const T* place = nullptr;
+  if (place_table != nullptr) {
+    int p = positions[row];
+    if (p < 0 || p >= places) {
+      if (threadIdx.x == 0 && error_flag != nullptr) atomicOr(error_flag, 4);
+      p = p < 0 ? 0 : places - 1;
+    }
+    place = place_table + (size_t)p * hidden;
+  }
+  float* dst = residual + (size_t)row * hidden;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_float(src[i]) * scale;
+    if (place != nullptr) v += to_float(place[i]);
+    dst[i] = v;
+    sum += v * v;
+  }
+  if (norm_weight == nullptr) return;
+  sum = block_sum(sum, scratch);
+  const float inv = 1.0f / sqrtf(sum / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = (dst[i] * inv) * norm_weight[i];   // every thread rereads what it wrote itself
+}
+
+// out[i] = act(in[i]), 32-bit inside: 0 the square of relu, 1 gelu in its tanh form, 2 silu.  In place is fine.
+__device__ __forceinline__ float activate(int kind, float z) {
+  if (kind == 0) {
+    const float r = fmaxf(z, 0.0f);
+    return r * r;
+  }
+  if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, int kind, size_t count) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_float<T>(activate(kind, to_float(in[i])));
+}
+
+template <typename T>
+__global__ void activation_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int kind, size_t count4) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = Vec4<T>::load(in + i * 4);
+    Vec4<T>::store(out + i * 4, make_float4(activate(kind, v.x), activate(kind, v.y), activate(kind, v.z), activate(kind, v.w)));
+  }
+}
+
 }  // namespace tlie
 
 using namespace tlie;
@@ -303,3 +367,35 @@ TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int row
   return (int)cudaGetLastError();
 }
 
+TLIE_EXPORT int tlie_embedding_positions(int dtype, const void* table, const void* place_table, const int* ids, const int* positions,
+                                         const float* norm_weight, float eps, float scale, float* residual, int rows, int hidden, int vocab,
+                                         int places, int* error_flag, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || (place_table != nullptr && (places <= 0 || positions == nullptr))) return (int)cudaErrorInvalidValue;
+  const int block = hidden >= 1024 ? 256 : 128;
+  if (dtype == TLIE_F32)
+    embedding_positions_kernel<float><<<rows, block, 0, stream>>>((const float*)table, (const float*)place_table, ids, positions, norm_weight, eps, scale,
+                                                                 residual, hidden, vocab, places, error_flag);
+  else
+    embedding_positions_kernel<__nv_bfloat16><<<rows, block, 0, stream>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)place_table, ids, positions,
+                                                                         norm_weight, eps, scale, residual, hidden, vocab, places, error_flag);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_activation(int dtype, int kind, const void* in, void* out, long long count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (kind < 0 || kind > 2) return (int)cudaErrorInvalidValue;
+  if (count % 4 == 0) {
+    const size_t count4 = (size_t)count / 4;
+    if (dtype == TLIE_F32)
+      activation_vec_kernel<float><<<grid_for(count4, 256), 256, 0, stream>>>((const float*)in, (float*)out, kind, count4);
+    else
+      activation_vec_kernel<__nv_bfloat16><<<grid_for(count4, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, kind, count4);
+    return (int)cudaGetLastError();
+  }
+  if (dtype == TLIE_F32)
+    activation_kernel<float><<<grid_for(count, 256), 256, 0, stream>>>((const float*)in, (float*)out, kind, (size_t)count);
+  else
+    activation_kernel<__nv_bfloat16><<<grid_for(count, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, kind, (size_t)count);
+  return (int)cudaGetLastError();
+}

@@ -25,7 +25,7 @@ from ..config import EngineConfig
 from ..errors import EngineError
 from .batch import StepEntry
 
-REPLAY_LIVE_REQUESTS = 8
+REPLAY_LIVE_REQUESTS = 4    # state slots and block-table rows of a replay: few, so that slots are used again
 
 
 def replay_engine_config(dtype: str, max_tokens: int, page_size: int = 64, device: str = "cuda:0") -> EngineConfig:

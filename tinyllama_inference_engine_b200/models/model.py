@@ -54,7 +54,7 @@ class DecoderModel:
         """The complete residual stream of the step's rows, and a lazy final norm of it if the last block left one prepared."""
         from .. import ops
 
-        residual = self.embedding.forward(ctx.token_ids)
+        residual = self.embedding.forward(ctx.token_ids, ctx)
         pending = None
         order = self.spec.order
         for index, entry in enumerate(order):

@@ -19,6 +19,8 @@ from ..errors import KernelError
 from .build import build_library, load_library
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
+RECURRENT_SOURCES = ["recurrent.cu"]              # compiled when a model with a recurrent mixer is first stepped
+MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with a distance bias, mixed heads or an output gate
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 
@@ -34,7 +36,8 @@ def core():
 
 def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
-    return [build_library("tlie_core", CORE_SOURCES)] + fast.build_all()
+    return [build_library("tlie_core", CORE_SOURCES), build_library("tlie_recurrent", RECURRENT_SOURCES),
+            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES)] + fast.build_all()
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -88,7 +91,8 @@ def _i32(tensor: torch.Tensor | None, what: str) -> c_void_p:
 # embedding (row 0 was read instead).  The engine reads the word wherever it synchronises with the device anyway.
 _error_flags: dict[torch.device, torch.Tensor] = {}
 DEVICE_ERRORS = {1: "a bounded wait inside a tensor-core kernel gave up; the step's results are not valid",
-                 2: "a token id outside the vocabulary reached the embedding kernel (non-finite logits upstream?)"}
+                 2: "a token id outside the vocabulary reached the embedding kernel (non-finite logits upstream?)",
+                 4: "a position beyond the table of learned position vectors reached the embedding kernel"}
 
 
 def error_flag(device: torch.device) -> torch.Tensor:
@@ -122,6 +126,35 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) ->
         raise KernelError("embedding: the table's width is not the residual's", code="invalid_shape")
     _check(core().tlie_embedding(_code(table), _ptr(table), _i32(ids, "ids"), _ptr(residual), c_int(rows), c_int(hidden), c_int(table.shape[0]),
                                  _ptr(error_flag(residual.device)), _stream()), "embedding")
+
+
+def embedding_positions(table, place_table, ids, positions, norm_weight, eps: float, residual, scale: float = 1.0) -> None:
+    """residual[t] = norm(float(table[ids[t]]) * scale + float(place_table[positions[t]])), all in 32-bit, in one kernel.
+
+    ``place_table`` (learned vectors by position) and ``norm_weight`` (an RMS norm with ``eps`` inside the root) may each be None.
+    A position beyond the table reads its last row and sets bit 2 of the device's error word."""
+    rows, hidden = residual.shape
+    if table.shape[1] != hidden or (place_table is not None and (place_table.shape[1] != hidden or place_table.dtype != table.dtype)):
+        raise KernelError("embedding_positions: the tables' widths and dtypes must be the residual's width and each other's", code="invalid_shape")
+    if residual.dtype != torch.float32 or (norm_weight is not None and (norm_weight.dtype != torch.float32 or norm_weight.numel() != hidden)):
+        raise KernelError("embedding_positions: the residual stream and the norm weight are 32-bit", code="invalid_dtype")
+    _check(core().tlie_embedding_positions(_code(table), _ptr(table), _ptr(place_table), _i32(ids, "ids"), _i32(positions, "positions"), _ptr(norm_weight),
+                                           c_float(eps), c_float(scale), _ptr(residual), c_int(rows), c_int(hidden), c_int(table.shape[0]),
+                                           c_int(0 if place_table is None else place_table.shape[0]), _ptr(error_flag(residual.device)), _stream()),
+           "embedding_positions")
+
+
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(kind: str, x, out) -> None:
+    """out = act(x) element by element, 32-bit inside (``out`` may be ``x``): the square of relu, gelu in its tanh form
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), or silu."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"no activation {kind!r}; known: {sorted(ACTIVATIONS)}", code="invalid_argument")
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("activation: the output must have the input's shape and dtype", code="invalid_shape")
+    _check(core().tlie_activation(_code(x), c_int(ACTIVATIONS[kind]), _ptr(x), _ptr(out), c_longlong(x.numel()), _stream()), "activation")
 
 
 def add_rmsnorm(residual, delta, weight, eps: float, out, rows=None) -> None:
@@ -334,6 +367,91 @@ def attention_step(qkv, positions, token_seq, block_table, inv_freq, rotary_dim:
             return
     rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, q_heads, kv_heads, head_dim, page_size, write_cache)
     paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch)
+
+
+# --- recurrences ---------------------------------------------------------------------------
+GATED_RECURRENCE_MAX_RUNS = 32
+
+
+def recurrent():
+    return load_library("tlie_recurrent", RECURRENT_SOURCES)
+
+
+def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_rows: int) -> None:
+    """The minGRU recurrence over every entry's rows, from and into the entries' state slots.
+
+    ``zxg`` [T, 3 W]: the stacked product (gate, candidate and output-gate pre-activations); per channel
+    z = sigmoid(a + bias_z), u = x + bias_x, cand = u + 1/2 if u >= 0 else sigmoid(u), S = (1 - z) S + z cand,
+    out = S * silu(g).  ``state`` [slots, W] is 32-bit and is read at ``state_slots[entry]`` and left at the entry's last row.
+    ``max_rows``: the longest entry of the step (decides into how many runs the kernel cuts an entry)."""
+    tokens, width = out.shape
+    entries = state_slots.shape[0]
+    if zxg.shape != (tokens, 3 * width) or zxg.dtype != out.dtype:
+        raise KernelError("mingru_scan: the stacked product must be [rows, 3 * width] of the output's dtype", code="invalid_shape")
+    if state.dtype != torch.float32 or state.shape[1] != width or bias_z.dtype != torch.float32 or bias_x.dtype != torch.float32 or bias_z.numel() != width or bias_x.numel() != width:
+        raise KernelError("mingru_scan: state [slots, width] and the two biases [width] are 32-bit", code="invalid_dtype")
+    if seq_starts.shape[0] != entries + 1:
+        raise KernelError("mingru_scan: seq_starts holds one more word than there are entries", code="invalid_shape")
+    runs = 1 if max_rows <= 1 else min(GATED_RECURRENCE_MAX_RUNS, max(2, -(-max_rows // 16)))
+    _check(recurrent().tlie_mingru_scan(_code(zxg), _ptr(zxg), _ptr(bias_z), _ptr(bias_x), _ptr(state), _i32(seq_starts, "seq_starts"),
+                                        _i32(state_slots, "state_slots"), _ptr(out), c_int(entries), c_int(width), c_int(runs), _stream()), "mingru_scan")
+
+
+# --- attention with mixed heads --------------------------------------------------------------
+def mixed_attention():
+    return load_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES)
+
+
+def _plane_pointers(cache, heads: int, key_dim: int, value_dim: int):
+    """Where the key plane and the value plane of a layer's pages start, and each one's page stride in elements."""
+    if cache.pages is not None:   # equal planes: [pages, 2, heads, page_size, width]
+        pages = cache.pages
+        if pages.dim() != 5 or pages.shape[1] != 2 or tuple(pages.shape[2:]) != (heads, cache.page_size, key_dim) or key_dim != value_dim or not pages.is_contiguous():
+            raise KernelError("attention pages must be contiguous [pages, 2, kv heads, page size, width]", code="invalid_shape")
+        plane = heads * cache.page_size * key_dim
+        return pages, _ptr(pages), 2 * plane, c_void_p(pages.data_ptr() + plane * pages.element_size()), 2 * plane
+    k_pages, v_pages = cache.plane_pages
+    if tuple(k_pages.shape[1:]) != (heads, cache.page_size, key_dim) or tuple(v_pages.shape[1:]) != (heads, cache.page_size, value_dim) or k_pages.dtype != v_pages.dtype:
+        raise KernelError("attention planes must be [pages, kv heads, page size, key width] and [.., value width]", code="invalid_shape")
+    return k_pages, _ptr(k_pages), heads * cache.page_size * key_dim, _ptr(v_pages), heads * cache.page_size * value_dim
+
+
+def store_kv_planes(rows, k_offset: int, v_offset: int, positions, token_seq, cache, kv_heads: int, key_dim: int, value_dim: int) -> None:
+    """Copy every token's keys (``kv_heads * key_dim`` columns of ``rows`` from ``k_offset``) and values (from ``v_offset``) into the
+    pages its request holds for its position.  ``cache``: the layer's ``LayerCache`` (one tensor of two equal planes, or a tensor per plane)."""
+    pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
+    if pages.dtype != rows.dtype:
+        raise KernelError("store_kv_planes: pages and rows differ in dtype", code="invalid_dtype")
+    table = cache.block_table
+    _check(mixed_attention().tlie_store_kv_planes(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(k_offset), c_int(v_offset), _i32(positions, "positions"),
+                                                  _i32(token_seq, "token_seq"), _i32(table, "block_table"), c_int(table.shape[1]), k_ptr, c_longlong(k_stride),
+                                                  v_ptr, c_longlong(v_stride), c_int(rows.shape[0]), c_int(kv_heads), c_int(key_dim), c_int(value_dim),
+                                                  c_int(cache.page_size), _stream()), "store_kv_planes")
+
+
+def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                          window: int, scale: float, batch=None) -> None:
+    """Attention over the paged keys with a distance bias, the heads' scores mixed before the softmax, and an output gate.
+
+    ``rows`` [T, >= heads * key_dim]: each row starts with its query heads; ``gate_offset`` (>= 0) names the column where
+    ``heads * value_dim`` gate pre-activations start (the output is multiplied by their sigmoid), -1 for none.  Score of query
+    head g at position i for key j: (q . k) * scale - slopes[g] * (i - j) (``slopes`` 32-bit [heads] or None); head h then sees
+    sum_g mix[h, g] score_g (``mix`` 32-bit [heads, heads] or None); keys with 0 <= i - j (< window if window > 0) are visible."""
+    tokens = rows.shape[0]
+    if heads % kv_heads != 0 or out.shape != (tokens, heads * value_dim) or out.dtype != rows.dtype:
+        raise KernelError("mixed_heads_attention: out must be [rows, heads * value_dim] of the rows' dtype, heads a multiple of kv heads", code="invalid_shape")
+    for name, tensor, count in (("slopes", slopes, heads), ("mix", mix, heads * heads)):
+        if tensor is not None and (tensor.dtype != torch.float32 or tensor.numel() != count):
+            raise KernelError(f"mixed_heads_attention: {name} must be 32-bit with {count} elements", code="invalid_shape")
+    pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
+    if pages.dtype != rows.dtype:
+        raise KernelError("mixed_heads_attention: pages and rows differ in dtype", code="invalid_dtype")
+    table = cache.block_table
+    _check(mixed_attention().tlie_mixed_heads_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr,
+                                                        c_longlong(v_stride), _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"),
+                                                        c_int(table.shape[1]), _ptr(slopes), _ptr(mix), _ptr(out), c_int(tokens), c_int(heads), c_int(kv_heads),
+                                                        c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), _stream()),
+           "mixed_heads_attention")
 
 
 # --- sampling ------------------------------------------------------------------------------

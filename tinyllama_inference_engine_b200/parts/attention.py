@@ -1,4 +1,5 @@
-"""Grouped-query attention over the paged cache."""
+"""Attention over the paged cache: grouped-query attention with a position encoding, and attention whose heads are biased by
+distance, mixed before the softmax and gated after it."""
 from __future__ import annotations
 
 import torch
@@ -85,4 +86,90 @@ class Attention(Mixer):
         return out
 
 
+class MixedHeadsAttention(Mixer):
+    """Grouped heads without a rotation: positions enter through a distance bias, the heads' scores are mixed by a learned matrix
+    before the softmax, and the concatenated heads pass an output gate before the output projection.
+
+    Score of query head g at position i for key j: (q_g . k_j) * scale - slope_g (i - j); head h sees sum_g M[h, g] score_g;
+    key j is visible while 0 <= i - j (and i - j < window, if there is a window); an ordinary softmax over the visible keys;
+    out = W_o (concat_h(softmax_h . v) * sigmoid(W_gate x)).
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads`` (query head h reads key/value head h // (heads / kv heads)),
+    ``key_dim`` (queries and keys), ``value_dim``, ``scale``, ``window`` (0: every earlier token), ``distance_slopes``
+    (one slope per head, or None for no bias), ``mix_heads`` (tensor ``<prefix>.talk`` [heads, heads], row h mixing into head h),
+    ``output_gate`` (tensor ``<prefix>.g`` [heads * value_dim, hidden]).
+    tensors: ``<prefix>.q`` [heads * key_dim, hidden], ``<prefix>.k`` [kv * key_dim, hidden], ``<prefix>.v`` [kv * value_dim, hidden],
+    ``<prefix>.o`` [hidden, heads * value_dim]; no biases.  q, k, v and the gate are one stacked product.  Keys and values are
+    two planes of a page (of different widths if ``key_dim != value_dim``); scores, mix, softmax and the gate are 32-bit.
+    """
+
+    capturable = True
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+    prepares_next_norm = True
+
+    @classmethod
+    def _sizes(cls, spec: PartSpec) -> tuple[int, int, int, int, int]:
+        return int(spec["hidden_size"]), int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["key_dim"]), int(spec["value_dim"])
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden, heads, kv, key_dim, value_dim = cls._sizes(spec)
+        std = hidden ** -0.5
+        specs = [TensorSpec(f"{prefix}.q", (heads * key_dim, hidden), std=std), TensorSpec(f"{prefix}.k", (kv * key_dim, hidden), std=std),
+                 TensorSpec(f"{prefix}.v", (kv * value_dim, hidden), std=std)]
+        if spec.get("mix_heads"):
+            specs.append(TensorSpec(f"{prefix}.talk", (heads, heads), std=heads ** -0.5))
+        if spec.get("output_gate"):
+            specs.append(TensorSpec(f"{prefix}.g", (heads * value_dim, hidden), std=std))
+        return specs + [TensorSpec(f"{prefix}.o", (hidden, heads * value_dim), std=(heads * value_dim) ** -0.5)]
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        _, _, kv, key_dim, value_dim = cls._sizes(spec)
+        return CacheNeed("pages", window=int(spec.get("window", 0) or 0), planes=((kv, key_dim), (kv, value_dim)))
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden, self.heads, self.kv_heads, self.key_dim, self.value_dim = self._sizes(spec)
+        self.window = int(spec.get("window", 0) or 0)
+        self.scale = float(spec["scale"]) if spec.get("scale") is not None else self.key_dim ** -0.5
+        dtype = runtime.dtype
+        stacked = [weights.get(f"{prefix}.{n}", dtype) for n in ("q", "k", "v")]
+        self.k_offset = self.heads * self.key_dim
+        self.v_offset = self.k_offset + self.kv_heads * self.key_dim
+        self.gate_offset = -1
+        if spec.get("output_gate"):
+            self.gate_offset = self.v_offset + self.kv_heads * self.value_dim
+            stacked.append(weights.get(f"{prefix}.g", dtype))
+        self.w_in = torch.cat(stacked, dim=0).contiguous()
+        self.w_o = weights.get(f"{prefix}.o", dtype).contiguous()
+        slopes = spec.get("distance_slopes")
+        self.slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32, device=runtime.device)
+        self.mix = weights.get(f"{prefix}.talk", torch.float32).contiguous() if spec.get("mix_heads") else None
+
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_o)
+
+    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
+        ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
+        rows = ws.get("qkv_gate", tokens, self.w_in.shape[0], dtype)
+        if isinstance(x, ops.LazyNorm):
+            ops.norm_linear(x, self.w_in, rows)
+        else:
+            ops.linear(x, self.w_in, rows)
+        if cache.writes:
+            ops.store_kv_planes(rows, self.k_offset, self.v_offset, ctx.positions, ctx.token_seq, cache, self.kv_heads, self.key_dim, self.value_dim)
+        mixed = ws.get("attention", tokens, self.heads * self.value_dim, dtype)
+        ops.mixed_heads_attention(rows, self.gate_offset, ctx.positions, ctx.token_seq, cache, self.slopes, self.mix, mixed, self.heads, self.kv_heads,
+                                  self.key_dim, self.value_dim, self.window, self.scale, batch=ctx)
+        if accumulate_into is not None:
+            ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
+            return None
+        out = ws.get("mixer_out", tokens, self.hidden, dtype)
+        ops.linear(mixed, self.w_o, out)
+        return out
+
+
 register_part("mixer", "attention", Attention)
+register_part("mixer", "mixed_heads_attention", MixedHeadsAttention)

@@ -9,7 +9,8 @@ class PreNormResidualBlock(Block):
     """x -> x + mixer(norm(x)) -> x + feed_forward(norm(x))  (src/model.cpp:112-207).
 
     params: ``mixer``, ``feed_forward``, ``mixer_norm``, ``feed_forward_norm``
-    (PartSpecs) and the tensor-name suffix of each (``*_name``).
+    (PartSpecs) and the tensor-name suffix of each (``*_name``).  ``feed_forward`` may be
+    None: the layer is then x -> x + mixer(norm(x)) alone.
     The hidden state travels as (32-bit residual, output not yet added): each norm
     adds the pending output into the residual before normalising, which is the
     reference's separate add kernel (src/cuda/kernels.cu:208-215) fused into its
@@ -21,9 +22,14 @@ class PreNormResidualBlock(Block):
     capturable = True
 
     @classmethod
+    def _slots(cls, spec: PartSpec):
+        """The block's (slot, category) pairs; a block whose ``feed_forward`` is None is its first sublayer alone."""
+        return [pair for pair in cls._SLOTS if spec.get("feed_forward") is not None or not pair[0].startswith("feed_forward")]
+
+    @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         specs: list[TensorSpec] = []
-        for slot, category in cls._SLOTS:
+        for slot, category in cls._slots(spec):
             child = spec[slot]
             specs += part_class(category, child).tensor_specs(child, f"{prefix}.{spec[slot + '_name']}")
         return specs
@@ -34,7 +40,8 @@ class PreNormResidualBlock(Block):
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        for slot, category in self._SLOTS:
+        self.feed_forward = self.feed_forward_norm = None
+        for slot, category in self._slots(spec):
             setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{spec[slot + '_name']}", weights, runtime))
 
     accepts_next_norm = True
@@ -47,6 +54,8 @@ class PreNormResidualBlock(Block):
         from .. import ops
 
         fused = residual.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device)
+        if self.feed_forward is None:
+            return residual, norm_then_part(self.mixer_norm, self.mixer, residual, pending, fused, next_norm, ctx, cache)
         pending = norm_then_part(self.mixer_norm, self.mixer, residual, pending, fused, self.feed_forward_norm, ctx, cache)
         pending = norm_then_part(self.feed_forward_norm, self.feed_forward, residual, pending, fused, next_norm, ctx)
         return residual, pending

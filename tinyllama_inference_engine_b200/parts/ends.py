@@ -8,10 +8,15 @@ from .base import Part, register_part
 from .spec import PartSpec, TensorSpec
 
 
+def _tensor_name(spec: PartSpec) -> str:
+    """The part's own tensor: ``tensor`` if the spec names it in full, else ``<name>.weight``."""
+    return spec.get("tensor") or f"{spec['name']}.weight"
+
+
 class TokenEmbedding(Part):
     """hidden = table[token], a row copy without scaling (src/model.cpp:94-97).
 
-    params: ``vocab_size``, ``hidden_size``, ``name``.  The row is widened into the
+    params: ``vocab_size``, ``hidden_size``, ``name`` (the tensor is ``<name>.weight``, or ``tensor`` in full).  The row is widened into the
     32-bit residual stream by a gather kernel (the reference copies one row per token
     with a device memcpy, src/cuda/model.cu:572-576).
     """
@@ -21,16 +26,55 @@ class TokenEmbedding(Part):
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]))]
+        return [TensorSpec(_tensor_name(spec), (spec["vocab_size"], spec["hidden_size"]))]
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        self.table = weights.get(f"{spec['name']}.weight", runtime.dtype).contiguous()
+        self.table = weights.get(_tensor_name(spec), runtime.dtype).contiguous()
         self.hidden = int(spec["hidden_size"])
 
-    def forward(self, token_ids):
+    def forward(self, token_ids, ctx=None):
         residual = self.runtime.workspace.get("residual", token_ids.shape[0], self.hidden, torch.float32)
         ops.embedding(self.table, token_ids, residual)
+        return residual
+
+
+class PositionedEmbedding(Part):
+    """hidden = norm(table[token] * scale + places[position]): a learned vector per position added to the token's row, the sum
+    normalised before the first layer.
+
+    params: ``vocab_size``, ``hidden_size``, ``tensor`` (the token table's name), optional ``positions`` = {``tensor``,
+    ``max_positions``} (the table of position vectors [max_positions, hidden]; positions count from 0 in each request),
+    optional ``norm`` = {``tensor``, ``eps``} (an RMS norm of the sum with its own weight), optional ``scale`` (1.0).
+    Sum, statistics and result are 32-bit: the result is the residual stream.  One kernel.
+    """
+
+    capturable = True
+    category = "embedding"
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden = spec["hidden_size"]
+        specs = [TensorSpec(_tensor_name(spec), (spec["vocab_size"], hidden), std=1.0)]
+        if spec.get("positions"):
+            specs.append(TensorSpec(spec["positions"]["tensor"], (spec["positions"]["max_positions"], hidden), std=0.5))
+        if spec.get("norm"):
+            specs.append(TensorSpec(spec["norm"]["tensor"], (hidden,), init="norm", std=0.1))
+        return specs
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.table = weights.get(_tensor_name(spec), runtime.dtype).contiguous()
+        places, norm = spec.get("positions"), spec.get("norm")
+        self.places = weights.get(places["tensor"], runtime.dtype).contiguous() if places else None
+        self.norm_weight = weights.get(norm["tensor"], torch.float32).contiguous() if norm else None
+        self.eps = float(norm["eps"]) if norm else 0.0
+        self.scale = float(spec.get("scale", 1.0))
+
+    def forward(self, token_ids, ctx=None):
+        residual = self.runtime.workspace.get("residual", token_ids.shape[0], self.hidden, torch.float32)
+        ops.embedding_positions(self.table, self.places, token_ids, None if ctx is None else ctx.positions, self.norm_weight, self.eps, residual, self.scale)
         return residual
 
 
@@ -49,11 +93,11 @@ class LinearHead(Part):
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]), optional=bool(spec.get("tied_to")))]
+        return [TensorSpec(_tensor_name(spec), (spec["vocab_size"], spec["hidden_size"]), optional=bool(spec.get("tied_to")))]
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        own = f"{spec['name']}.weight"
+        own = _tensor_name(spec)
         source = own if not spec.get("tied_to") or weights.has(own) else f"{spec['tied_to']}.weight"
         self.weight = weights.get(source, runtime.dtype).contiguous()
         self.vocab = int(spec["vocab_size"])
@@ -70,4 +114,5 @@ class LinearHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "positioned_embedding", PositionedEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -1,4 +1,4 @@
-"""The gated feed-forward."""
+"""Feed-forwards: the gated one, and the plain one of two products with an activation between them."""
 from __future__ import annotations
 
 import torch
@@ -71,4 +71,59 @@ class GatedMLP(FeedForward):
         return out
 
 
+class DenseMLP(FeedForward):
+    """down( act(up(x)) ), no gate and no biases.
+
+    params: ``hidden_size``, ``intermediate_size``, ``activation`` ("relu_squared", "gelu_tanh" or "silu"; ops.ACTIVATIONS),
+    optional ``up_name`` / ``down_name`` (the tensors are ``<prefix>.<name>``: "up" and "down" unless given).
+    The activation is computed in 32-bit on the first product's output, in place.  With few rows the norm in front is applied
+    inside the first product and the residual add inside the second, as the gated feed-forward does.
+    """
+
+    capturable = True
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+    prepares_next_norm = True
+
+    @classmethod
+    def _names(cls, spec: PartSpec, prefix: str) -> tuple[str, str]:
+        return f"{prefix}.{spec.get('up_name', 'up')}", f"{prefix}.{spec.get('down_name', 'down')}"
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden, inter = spec["hidden_size"], spec["intermediate_size"]
+        up, down = cls._names(spec, prefix)
+        return [TensorSpec(up, (inter, hidden), std=hidden ** -0.5), TensorSpec(down, (hidden, inter), std=inter ** -0.5)]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.activation = spec.get("activation", "relu_squared")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ConfigError(f"dense_mlp has no activation {self.activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        up, down = self._names(spec, prefix)
+        self.w_up = weights.get(up, runtime.dtype).contiguous()
+        self.w_down = weights.get(down, runtime.dtype).contiguous()
+
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_down)
+
+    def forward(self, x, ctx, accumulate_into=None, prepare=None):
+        ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
+        act = ws.get("activated", tokens, self.inter, dtype)
+        if isinstance(x, ops.LazyNorm):
+            ops.norm_linear(x, self.w_up, act)
+        else:
+            ops.linear(x, self.w_up, act)
+        ops.activation(self.activation, act, act)
+        if accumulate_into is not None:
+            ops.linear_accumulate(act, self.w_down, accumulate_into, prepare)
+            return None
+        out = ws.get("ff_out", tokens, self.hidden, dtype)
+        ops.linear(act, self.w_down, out)
+        return out
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "dense_mlp", DenseMLP)

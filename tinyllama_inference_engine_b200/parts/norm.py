@@ -11,7 +11,8 @@ from .spec import PartSpec, TensorSpec
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * weight, eps inside the root (src/operators.cpp:22-45).
 
-    params: ``size``, ``eps``.  tensors: ``<prefix>.weight [size]``.
+    params: ``size``, ``eps``, optional ``suffix`` (what follows the prefix in the tensor's name, ".weight" unless given).
+    tensors: ``<prefix><suffix> [size]``.
     The statistics, the scale and the residual sum are 32-bit in both precisions;
     the weight is held in 32-bit (exact for a bfloat16 checkpoint).
     """
@@ -21,13 +22,13 @@ class RMSNorm(Norm):
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        return [TensorSpec(f"{prefix}.weight", (spec["size"],), init="norm", std=0.1)]
+        return [TensorSpec(f"{prefix}{spec.get('suffix', '.weight')}", (spec["size"],), init="norm", std=0.1)]
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
-        self.weight = weights.get(f"{prefix}.weight", torch.float32).contiguous()
+        self.weight = weights.get(f"{prefix}{spec.get('suffix', '.weight')}", torch.float32).contiguous()
 
     def forward(self, residual, delta=None, rows=None, lazy: bool = False):
         """``lazy`` (and nothing to add): hand the norm on to the product that consumes it (ops.LazyNorm)."""
