@@ -173,7 +173,8 @@ def store_kv_planes(rows, k_offset, v_offset, positions, token_seq, cache, kv_he
         v_pages[page, :, pos % cache.page_size, :] = rows[t, v_offset : v_offset + kv_heads * value_dim].view(kv_heads, value_dim)
 
 
-def mixed_heads_attention(rows, gate_offset, positions, token_seq, cache, slopes, mix, out, heads, kv_heads, key_dim, value_dim, window, scale, batch=None) -> None:
+def mixed_heads_attention(rows, gate_offset, positions, token_seq, cache, slopes, mix, out, heads, kv_heads, key_dim, value_dim, window, scale, batch=None,
+                          folded_slopes=None) -> None:
     k_pages, v_pages = _planes(cache)
     tokens, group, size = rows.shape[0], heads // kv_heads, cache.page_size
     result = torch.zeros(tokens, heads * value_dim)

@@ -197,50 +197,94 @@ def test_mingru_scan_kernel(dtype, atol, width, lens):
     assert torch.equal(got_state.cpu()[untouched], state[untouched])
 
 
-@pytest.mark.gpu
-@pytest.mark.parametrize("dtype,atol", [(torch.float32, 3e-6), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("heads,kv,key_dim,value_dim,window,bias,mix,gate", [
-    (4, 2, 16, 16, 20, True, True, True), (4, 2, 16, 24, 0, True, True, True), (3, 3, 8, 8, 7, False, True, False), (6, 1, 32, 16, 33, True, False, True),
-    (1, 1, 12, 20, 1, True, True, True), (8, 4, 96, 96, 16, True, True, True), (5, 5, 10, 6, 17, False, False, False),
-])
-def test_mixed_heads_attention_kernel(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate):
-    """Rows of three requests at different positions, pages handed out in a scrambled order; every option on and off."""
-    from tinyllama_inference_engine_b200 import ops
+def _attention_case(dtype, heads, kv, key_dim, value_dim, lens, firsts, gate, page_size=16):
+    """Rows of some requests at given positions over pages handed out in a scrambled order; returns what both implementations take."""
+    from types import SimpleNamespace
+
     from tinyllama_inference_engine_b200.parts.base import CacheNeed, LayerCache
 
-    g = torch.Generator().manual_seed(heads * 100 + key_dim)
-    page_size, lens, firsts = 16, [37, 1, 18], [0, 52, 30]       # the second is a decoded token, the third a portion that starts inside a page
-    order = torch.randperm(24, generator=g).tolist()
-    table = torch.full((3, 8), -1, dtype=torch.int32)
+    g = torch.Generator().manual_seed(heads * 100 + key_dim + len(lens))
+    width = max(-(-(f + n) // page_size) for n, f in zip(lens, firsts))
+    count = sum(-(-(f + n) // page_size) for n, f in zip(lens, firsts)) + 3
+    order = torch.randperm(count, generator=g).tolist()
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
     for r, (n, f) in enumerate(zip(lens, firsts)):
         for p in range(-(-(f + n) // page_size)):
             table[r, p] = order.pop()
     columns = heads * key_dim + kv * key_dim + kv * value_dim + (heads * value_dim if gate else 0)
     if key_dim == value_dim:
-        pages = torch.randn(24, 2, kv, page_size, key_dim, generator=g).to(dtype)
+        pages = torch.randn(count, 2, kv, page_size, key_dim, generator=g).to(dtype)
         cpu_cache = LayerCache(CacheNeed("pages"), True, pages, table, page_size)
         gpu_cache = LayerCache(CacheNeed("pages"), True, pages.cuda(), table.cuda(), page_size)
     else:
-        planes = (torch.randn(24, kv, page_size, key_dim, generator=g).to(dtype), torch.randn(24, kv, page_size, value_dim, generator=g).to(dtype))
+        planes = (torch.randn(count, kv, page_size, key_dim, generator=g).to(dtype), torch.randn(count, kv, page_size, value_dim, generator=g).to(dtype))
         cpu_cache = LayerCache(CacheNeed("pages"), True, None, table, page_size, None, planes)
         gpu_cache = LayerCache(CacheNeed("pages"), True, None, table.cuda(), page_size, None, tuple(p.cuda() for p in planes))
     rows = torch.randn(sum(lens), columns, generator=g).to(dtype)
     positions = torch.tensor([f + i for n, f in zip(lens, firsts) for i in range(n)], dtype=torch.int32)
     token_seq = torch.tensor([r for r, n in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    batch = SimpleNamespace(max_q_len=max(lens), num_seqs=len(lens), max_seq_len=max(f + n for n, f in zip(lens, firsts)), seq_starts=starts.cuda(),
+                            first_positions=torch.tensor(firsts, dtype=torch.int32).cuda(), num_tokens=sum(lens))
+    mixing = torch.randn(heads, heads, generator=g) * 0.6
+    return rows, positions, token_seq, cpu_cache, gpu_cache, batch, mixing
+
+
+def _compare_attention(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate, lens, firsts, with_batch):
+    from tinyllama_inference_engine_b200 import ops
+
+    rows, positions, token_seq, cpu_cache, gpu_cache, batch, mixing = _attention_case(dtype, heads, kv, key_dim, value_dim, lens, firsts, gate)
     slopes = torch.tensor(plain_marutar.head_slopes(heads).tolist(), dtype=torch.float32) if bias else None
-    mixing = torch.randn(heads, heads, generator=g) * 0.6 if mix else None
+    mixing = mixing if mix else None
     k_offset, v_offset = heads * key_dim, heads * key_dim + kv * key_dim
     gate_offset = v_offset + kv * value_dim if gate else -1
     want = torch.zeros(sum(lens), heads * value_dim, dtype=dtype)
     plain_ops.store_kv_planes(rows, k_offset, v_offset, positions, token_seq, cpu_cache, kv, key_dim, value_dim)
     plain_ops.mixed_heads_attention(rows, gate_offset, positions, token_seq, cpu_cache, slopes, mixing, want, heads, kv, key_dim, value_dim, window, 0.3)
     got = torch.zeros(sum(lens), heads * value_dim, dtype=dtype, device="cuda")
+    before = ops.launch_count
     ops.store_kv_planes(rows.cuda(), k_offset, v_offset, positions.cuda(), token_seq.cuda(), gpu_cache, kv, key_dim, value_dim)
     ops.mixed_heads_attention(rows.cuda(), gate_offset, positions.cuda(), token_seq.cuda(), gpu_cache, _cuda(slopes), _cuda(mixing), got, heads, kv, key_dim,
-                              value_dim, window, 0.3)
+                              value_dim, window, 0.3, batch=batch if with_batch else None)
     for mine, theirs in zip([gpu_cache.pages] if key_dim == value_dim else gpu_cache.plane_pages, [cpu_cache.pages] if key_dim == value_dim else cpu_cache.plane_pages):
         assert torch.equal(mine.cpu(), theirs)
     assert float((got.cpu().float() - want.float()).abs().max()) <= atol * max(1.0, float(want.float().abs().max()))
+    return ops.launch_count - before
+
+
+ATTENTION_SHAPES = [
+    (4, 2, 16, 16, 20, True, True, True), (4, 2, 16, 24, 0, True, True, True), (3, 3, 8, 8, 7, False, True, False), (6, 1, 32, 16, 33, True, False, True),
+    (1, 1, 12, 20, 1, True, True, True), (8, 4, 96, 96, 16, True, True, True), (5, 5, 10, 6, 17, False, False, False),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,atol", [(torch.float32, 3e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("heads,kv,key_dim,value_dim,window,bias,mix,gate", ATTENTION_SHAPES)
+def test_mixed_heads_attention_kernel(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate):
+    """The general kernel: a portion from position 0, a decoded token, and a portion that starts inside a page; every option on and off."""
+    _compare_attention(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate, [37, 1, 18], [0, 52, 30], with_batch=False)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,kv,key_dim,value_dim,window,bias,mix,gate", [
+    (4, 2, 16, 16, 20, True, True, True), (8, 4, 96, 96, 16, True, True, True), (6, 1, 32, 16, 33, True, False, True), (4, 2, 16, 32, 0, True, True, False),
+    (2, 2, 48, 48, 70, False, True, True), (3, 1, 64, 64, 64, True, True, True), (6, 3, 32, 48, 1, True, True, True), (4, 4, 64, 16, 129, False, False, False),
+])
+def test_mixed_heads_attention_on_tensor_cores(heads, kv, key_dim, value_dim, window, bias, mix, gate):
+    """The prompt kernel (mix folded into the queries, flash attention over the concatenated key heads): portions that start at 0, inside
+    a page and far into a request, of 1 to 150 rows, against the plain function; the step's shape makes the wrapper choose it."""
+    launches = _compare_attention(torch.bfloat16, 1.6e-2, heads, kv, key_dim, value_dim, window, bias, mix, gate, [1, 150, 18, 70, 1], [77, 0, 30, 215, 3], with_batch=True)
+    assert launches == 3      # the store, the fold and the attention: not the general kernel
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,atol", [(torch.float32, 3e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("heads,kv,key_dim,value_dim,window,bias,mix,gate", [(4, 2, 16, 16, 300, True, True, True), (8, 4, 96, 96, 0, True, True, True),
+                                                                             (3, 1, 24, 40, 0, True, True, True)])
+def test_mixed_heads_attention_with_rows_cut_over_ctas(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate):
+    """Decoded tokens over long contexts: each row's keys are dealt to several CTAs and merged; rows at 3 and 40 keys leave CTAs empty."""
+    _compare_attention(dtype, atol, heads, kv, key_dim, value_dim, window, bias, mix, gate, [1, 1, 1, 1], [700, 3, 1029, 40], with_batch=True)
 
 
 @pytest.mark.gpu

@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     const T* __restrict__ rows, int row_stride, int gate_offset, const T* __restrict__ k_pages, long long k_page_stride,
     const T* __restrict__ v_pages, long long v_page_stride, const int* __restrict__ positions, const int* __restrict__ token_seq,
     const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, const float* __restrict__ mix, T* __restrict__ out,
-    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale) {
+    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_bytes[];
   long long* k_at = reinterpret_cast<long long*>(smem_bytes);   // [32] where a key's row starts in its plane (head 0)
   long long* v_at = k_at + kMixKeys;
@@ -123,8 +123,15 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
   }
 
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  for (int base = lo; base <= pos; base += kMixKeys) {
-    const int count = min(kMixKeys, pos - base + 1);
+  // With gridDim.y > 1 the row's key tiles are dealt to that many CTAs in runs; each leaves its unnormalised sums, maxima and
+  // totals in ``partial`` and merge_mixed_kernel puts them together.
+  const int splits = gridDim.y;
+  const int tiles = (pos - lo) / kMixKeys + 1;
+  const int tiles_each = (tiles + splits - 1) / splits;
+  const int first_key = lo + blockIdx.y * tiles_each * kMixKeys;
+  const int last_key = min(pos, first_key + tiles_each * kMixKeys - 1);
+  for (int base = first_key; base <= last_key; base += kMixKeys) {
+    const int count = min(kMixKeys, last_key - base + 1);
     __syncthreads();   // the tile before is done with k_at / v_at (and, the first time, q_s and the running sums are in place)
     if (tid < count) {
       const int key = base + tid;
@@ -180,6 +187,19 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     }
   }
   __syncthreads();
+  if (splits > 1) {
+    float* mine = partial + ((size_t)t * splits + blockIdx.y) * (outputs + 2 * heads);
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) {
+      const int o = tid + i * kMixThreads;
+      if (o < outputs) mine[o] = acc[i];
+    }
+    for (int i = tid; i < heads; i += kMixThreads) {
+      mine[outputs + i] = max_s[i];
+      mine[outputs + heads + i] = sum_s[i];
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < ACC; ++i) {
     const int o = tid + i * kMixThreads;
@@ -194,19 +214,48 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
   }
 }
 
+// The parts of a row put together: out = sum_s acc_s e^(max_s - max) / sum_s total_s e^(max_s - max), then the gate.
+template <typename T>
+__global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* __restrict__ rows, int row_stride, int gate_offset, T* __restrict__ out,
+                                   int heads, int value_dim, int splits) {
+  const int t = blockIdx.x;
+  const int outputs = heads * value_dim;
+  const float* mine = partial + (size_t)t * splits * (outputs + 2 * heads);
+  for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+    const int h = o / value_dim;
+    float highest = -INFINITY;
+    for (int s = 0; s < splits; ++s) highest = fmaxf(highest, mine[(size_t)s * (outputs + 2 * heads) + outputs + h]);
+    float value = 0.0f, total = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      const float* part = mine + (size_t)s * (outputs + 2 * heads);
+      const float weight = expf(part[outputs + h] - highest);   // a part that saw no key has maximum -inf: weight 0
+      value += part[o] * weight;
+      total += part[outputs + heads + h] * weight;
+    }
+    float v = value / total;
+    if (gate_offset >= 0) {
+      const float g = to_float(rows[(size_t)t * row_stride + gate_offset + o]);
+      v *= 1.0f / (1.0f + expf(-g));
+    }
+    out[(size_t)t * outputs + o] = from_float<T>(v);
+  }
+}
+
 template <typename T, int ACC>
 static int launch_mixed(const void* rows, int row_stride, int gate_offset, const void* k_pages, long long k_page_stride, const void* v_pages,
                         long long v_page_stride, const int* positions, const int* token_seq, const int* block_table, int table_stride,
                         const float* slopes, const float* mix, void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
-                        int page_size, int window, float scale, size_t smem, cudaStream_t stream) {
+                        int page_size, int window, float scale, size_t smem, int splits, float* partial, cudaStream_t stream) {
   auto kernel = mixed_heads_attention_kernel<T, ACC>;
   if (smem > 48 * 1024) {
     const cudaError_t set = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (set != cudaSuccess) return (int)set;
   }
-  kernel<<<tokens, kMixThreads, smem, stream>>>((const T*)rows, row_stride, gate_offset, (const T*)k_pages, k_page_stride, (const T*)v_pages,
-                                                v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
-                                                kv_heads, key_dim, value_dim, page_size, window, scale);
+  kernel<<<dim3(tokens, splits), kMixThreads, smem, stream>>>((const T*)rows, row_stride, gate_offset, (const T*)k_pages, k_page_stride, (const T*)v_pages,
+                                                              v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
+                                                              kv_heads, key_dim, value_dim, page_size, window, scale, partial);
+  if (splits > 1)
+    merge_mixed_kernel<T><<<tokens, 256, 0, stream>>>(partial, (const T*)rows, row_stride, gate_offset, (T*)out, heads, value_dim, splits);
   return (int)cudaGetLastError();
 }
 
@@ -230,14 +279,16 @@ TLIE_EXPORT int tlie_store_kv_planes(int dtype, const void* rows, int row_stride
   return (int)cudaGetLastError();
 }
 
-// ``gate_offset`` < 0: no output gate.  ``slopes`` / ``mix`` null: no distance bias / heads left as they are.
+// ``gate_offset`` < 0: no output gate.  ``slopes`` / ``mix`` null: no distance bias / heads left as they are.  ``splits`` > 1: every row's
+// keys are dealt to that many CTAs (steps of few rows and long contexts); ``partial`` then holds tokens * splits * (heads * value_dim + 2 * heads) floats.
 TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_stride, int gate_offset, const void* k_pages,
                                            long long k_page_stride, const void* v_pages, long long v_page_stride, const int* positions,
                                            const int* token_seq, const int* block_table, int table_stride, const float* slopes, const float* mix,
                                            void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window,
-                                           float scale, cudaStream_t stream) {
+                                           float scale, int splits, float* partial, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0) return (int)cudaErrorInvalidValue;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0 || splits < 1 || splits > 65535 || (splits > 1 && partial == nullptr))
+    return (int)cudaErrorInvalidValue;
   const int outputs = heads * value_dim;
   if (outputs > 32 * kMixThreads) return (int)cudaErrorInvalidValue;
   const size_t floats = (size_t)heads * key_dim + (mix ? (size_t)heads * heads : 0) + 2 * (size_t)heads * kMixKeys + 3 * (size_t)heads;
@@ -245,7 +296,7 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
 #define TLIE_MIXED(T, ACC)                                                                                                                    \
   return launch_mixed<T, ACC>(rows, row_stride, gate_offset, k_pages, k_page_stride, v_pages, v_page_stride, positions, token_seq, block_table, \
-                              table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, stream)
+                              table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, splits, partial, stream)
   if (dtype == TLIE_F32) {
     if (outputs <= 4 * kMixThreads) TLIE_MIXED(float, 4);
     if (outputs <= 16 * kMixThreads) TLIE_MIXED(float, 16);

@@ -1,0 +1,319 @@
+// Attention with mixed heads for prompt portions on the tensor cores, bfloat16 (the mathematics of attention_mixed.cu).
+//
+// The mix is linear in the raw scores, so it can be applied to the queries instead of the scores:
+//   mixed_h(i, j) = sum_g M[h, g] ((q_g . k_{c(g)}) * scale - slope_g (i - j))
+//                 = sum_c Q'_{h, c} . k_c(j)  -  slope'_h (i - j)
+// with Q'_{h, c} = scale * sum_{g in group c} M[h, g] q_g (one folded query per head and key/value head, made by
+// fold_queries_kernel in 32-bit and rounded to bfloat16 once) and slope'_h = sum_g M[h, g] slope_g (made on the host).  Head h
+// is then ordinary flash attention whose query is the concatenation of its PARTS folded queries and whose key is the
+// concatenation of the token's PARTS key heads: nothing of the scores is ever mixed outside the tensor cores.  Without a mix
+// PARTS is 1 and the query is the head's own.
+//
+// One CTA per (tile of rows of one request, head), one warp per 16 rows; keys and values stream through shared memory in
+// 64-key tiles (cp.async, two stages where they fit); Q'.K^T and P.V on mma.sync m16n8k16 with 32-bit accumulators, the
+// distance bias, the mask, the running maximum and sum in 32-bit; the output gate in the epilogue.
+//
+// Compile-time: KEY_DIM, VALUE_DIM (multiples of 16), PARTS (key heads per folded query).
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+#ifndef KEY_DIM
+#define KEY_DIM 64
+#endif
+#ifndef VALUE_DIM
+#define VALUE_DIM 64
+#endif
+#ifndef PARTS
+#define PARTS 1
+#endif
+
+namespace tlie {
+
+constexpr int kD = KEY_DIM, kVD = VALUE_DIM, kParts = PARTS;
+constexpr int kKeys = 64;
+constexpr int kKRow = kD + 8, kVRow = kVD + 8, kQRow = kParts * kD + 8;   // padded shared-memory rows (elements)
+constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t smem_for(int rows, int stages) {
+  return ((size_t)rows * kQRow + (size_t)stages * ((size_t)kParts * kKeys * kKRow + (size_t)kKeys * kVRow)) * sizeof(__nv_bfloat16);
+}
+constexpr bool fits(int rows, int stages) { return smem_for(rows, stages) <= kSmemLimit; }
+// rows per CTA and stages: the largest that fits shared memory; 0 rows if nothing does (the host then uses the general kernel)
+constexpr int kRows = fits(64, 2) ? 64 : fits(32, 2) ? 32 : fits(64, 1) ? 64 : fits(32, 1) ? 32 : fits(16, 1) ? 16 : 0;
+constexpr int kStages = (fits(64, 2) || fits(32, 2)) ? 2 : 1;
+constexpr int kWarps = kRows > 0 ? kRows / 16 : 1;
+constexpr int kThreads = kWarps * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// folded[t, h, p, :] = scale * sum over the query heads g of key/value head c(p) of M[h, g] q[t, g, :]   (no mix: scale * q[t, h, :])
+__global__ void fold_queries_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, const float* __restrict__ mix, float scale,
+                                    __nv_bfloat16* __restrict__ folded, int heads, int group) {
+  const int t = blockIdx.x;
+  const __nv_bfloat16* q = rows + (size_t)t * row_stride;
+  __nv_bfloat16* dst = folded + (size_t)t * heads * kParts * kD;
+  for (int i = threadIdx.x; i < heads * kParts * kD; i += blockDim.x) {
+    const int d = i % kD, p = (i / kD) % kParts, h = i / (kD * kParts);
+    float sum;
+    if (mix == nullptr) {
+      sum = __bfloat162float(q[h * kD + d]);
+    } else {
+      sum = 0.0f;
+      for (int g = p * group; g < (p + 1) * group; ++g) sum += mix[h * heads + g] * __bfloat162float(q[g * kD + d]);
+    }
+    dst[i] = __float2bfloat16_rn(sum * scale);
+  }
+}
+
+__device__ __forceinline__ void load_tile(__nv_bfloat16* k_smem, __nv_bfloat16* v_smem, const __nv_bfloat16* k_pages, long long k_page_stride,
+                                          const __nv_bfloat16* v_pages, long long v_page_stride, const int* table, int key0, int lo, int n_keys,
+                                          int kvh, int page_size, bool mixed) {
+  // a page holds a multiple of 16 keys, so each 16-key quarter of a tile lies in one page
+  long long page_of[kKeys / 16];
+  int slot_of[kKeys / 16];
+#pragma unroll
+  for (int h = 0; h < kKeys / 16; ++h) {
+    const int k = key0 + 16 * h;
+    const bool any = k < n_keys && k + 16 > lo;
+    page_of[h] = any ? table[k / page_size] : 0;
+    slot_of[h] = k % page_size;
+  }
+  constexpr int kChunks = kD / 8, kVChunks = kVD / 8;
+  for (int idx = threadIdx.x; idx < kParts * kKeys * kChunks; idx += kThreads) {
+    const int chunk = idx % kChunks, row = (idx / kChunks) % kKeys, part = idx / (kChunks * kKeys);
+    const int key = key0 + row, quarter = row >> 4;
+    const bool valid = key >= lo && key < n_keys;
+    const int head = mixed ? part : kvh;
+    const long long page = quarter == 0 ? page_of[0] : quarter == 1 ? page_of[1] : quarter == 2 ? page_of[2] : page_of[3];
+    const int slot = (quarter == 0 ? slot_of[0] : quarter == 1 ? slot_of[1] : quarter == 2 ? slot_of[2] : slot_of[3]) + (row & 15);
+    const __nv_bfloat16* src = k_pages + page * k_page_stride + ((size_t)head * page_size + slot) * kD + chunk * 8;
+    cp_async_16(k_smem + ((size_t)part * kKeys + row) * kKRow + chunk * 8, valid ? src : k_pages, valid);
+  }
+  for (int idx = threadIdx.x; idx < kKeys * kVChunks; idx += kThreads) {
+    const int chunk = idx % kVChunks, row = idx / kVChunks;
+    const int key = key0 + row, quarter = row >> 4;
+    const bool valid = key >= lo && key < n_keys;
+    const long long page = quarter == 0 ? page_of[0] : quarter == 1 ? page_of[1] : quarter == 2 ? page_of[2] : page_of[3];
+    const int slot = (quarter == 0 ? slot_of[0] : quarter == 1 ? slot_of[1] : quarter == 2 ? slot_of[2] : slot_of[3]) + (row & 15);
+    const __nv_bfloat16* src = v_pages + page * v_page_stride + ((size_t)kvh * page_size + slot) * kVD + chunk * 8;
+    cp_async_16(v_smem + (size_t)row * kVRow + chunk * 8, valid ? src : v_pages, valid);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    mixed_prefill_kernel(const __nv_bfloat16* __restrict__ folded, const __nv_bfloat16* __restrict__ rows, int row_stride, int gate_offset,
+                         const __nv_bfloat16* __restrict__ k_pages, long long k_page_stride, const __nv_bfloat16* __restrict__ v_pages,
+                         long long v_page_stride, const int* __restrict__ seq_starts, const int* __restrict__ first_positions,
+                         const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, __nv_bfloat16* __restrict__ out,
+                         int heads, int kv_heads, int page_size, int window, int mixed) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kRows][kQRow]
+  __nv_bfloat16* kv_smem = q_smem + (size_t)kRows * kQRow;                       // [stages]{K [parts][64][kKRow], V [64][kVRow]}
+  constexpr size_t kStage = (size_t)kParts * kKeys * kKRow + (size_t)kKeys * kVRow;
+  const int seq = blockIdx.y, head = blockIdx.z;
+  const int seq_start = seq_starts[seq];
+  const int q_len = seq_starts[seq + 1] - seq_start;
+  const int row_in_seq = (gridDim.x - 1 - blockIdx.x) * kRows;   // later tiles see more keys: they start first
+  if (row_in_seq >= q_len) return;
+  const int row0 = seq_start + row_in_seq;
+  const int kvh = head / (heads / kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int rows_here = min(kRows, q_len - row_in_seq);
+  const int pos0 = first_positions[seq] + row_in_seq;
+  const int last_pos = pos0 + rows_here - 1;
+  const int n_keys = last_pos + 1;
+  const int lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int* table = block_table + (size_t)seq * table_stride;
+  const float slope = slopes ? slopes[head] * kLog2e : 0.0f;
+
+  constexpr int kQChunks = kParts * kD / 8;
+  for (int idx = threadIdx.x; idx < kRows * kQChunks; idx += kThreads) {
+    const int row = idx / kQChunks, chunk = idx - row * kQChunks;
+    const bool valid = row < rows_here;
+    const __nv_bfloat16* src = folded + ((size_t)(row0 + (valid ? row : 0)) * heads + head) * (kParts * kD) + chunk * 8;
+    cp_async_16(q_smem + (size_t)row * kQRow + chunk * 8, src, valid);
+  }
+  cp_async_commit();
+
+  const int first_tile = lo_tile / kKeys;
+  const int end_tile = (n_keys + kKeys - 1) / kKeys;
+  auto stage_k = [&](int s) { return kv_smem + (size_t)s * kStage; };
+  auto stage_v = [&](int s) { return kv_smem + (size_t)s * kStage + (size_t)kParts * kKeys * kKRow; };
+  if (kStages == 2) {
+    load_tile(stage_k(0), stage_v(0), k_pages, k_page_stride, v_pages, v_page_stride, table, first_tile * kKeys, lo_tile, n_keys, kvh, page_size, mixed != 0);
+    cp_async_commit();
+  }
+
+  const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
+  int my_pos[2], my_lo[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    my_pos[r] = pos0 + min(my_row[r], rows_here - 1);   // rows past the end behave like the last row; never stored
+    my_lo[r] = (window > 0 && my_pos[r] - window + 1 > 0) ? my_pos[r] - window + 1 : 0;
+  }
+  float o[kVD / 8][4];
+#pragma unroll
+  for (int i = 0; i < kVD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY};
+  float row_sum[2] = {0.0f, 0.0f};
+
+  for (int tile = first_tile; tile < end_tile; ++tile) {
+    int stage = 0;
+    if (kStages == 2) {
+      stage = (tile - first_tile) & 1;
+      if (tile + 1 < end_tile)
+        load_tile(stage_k(stage ^ 1), stage_v(stage ^ 1), k_pages, k_page_stride, v_pages, v_page_stride, table, (tile + 1) * kKeys, lo_tile, n_keys, kvh,
+                  page_size, mixed != 0);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      load_tile(stage_k(0), stage_v(0), k_pages, k_page_stride, v_pages, v_page_stride, table, tile * kKeys, lo_tile, n_keys, kvh, page_size, mixed != 0);
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const __nv_bfloat16* k_smem = stage_k(stage);
+    const __nv_bfloat16* v_smem = stage_v(stage);
+    const int key0 = tile * kKeys;
+    const int warp_last_pos = pos0 + min(warp * 16 + 15, rows_here - 1);
+    const int warp_first_pos = pos0 + min(warp * 16, rows_here - 1);
+    const int warp_lo = (window > 0 && warp_first_pos - window + 1 > 0) ? warp_first_pos - window + 1 : 0;
+    if (key0 <= warp_last_pos && key0 + kKeys > warp_lo) {   // some row of this warp sees some key of this tile
+      float s_frag[kKeys / 8][4];
+#pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j) s_frag[j][0] = s_frag[j][1] = s_frag[j][2] = s_frag[j][3] = 0.0f;
+#pragma unroll 1
+      for (int part = 0; part < kParts; ++part) {
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          unsigned qa[4];
+          ldmatrix_x4(qa, q_smem + (size_t)(warp * 16 + (lane & 15)) * kQRow + part * kD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int jp = 0; jp < kKeys / 16; ++jp) {
+            unsigned b[4];
+            const int row = (jp * 2 + (lane >> 4)) * 8 + (lane & 7);
+            const int col = ks * 16 + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4(b, k_smem + ((size_t)part * kKeys + row) * kKRow + col);
+            mma_bf16(s_frag[jp * 2], qa, b[0], b[1]);
+            mma_bf16(s_frag[jp * 2 + 1], qa, b[2], b[3]);
+          }
+        }
+      }
+      // scores in units of log2: (dot - slope (i - j)) log2 e; keys outside a row's window or after it are masked
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + j * 8 + 2 * t + (e & 1);
+          const int r = e >> 1;
+          const float v = (key >= my_lo[r] && key <= my_pos[r]) ? fmaf(s_frag[j][e], kLog2e, -slope * (float)(my_pos[r] - key)) : -INFINITY;
+          s_frag[j][e] = v;
+          tile_max[r] = fmaxf(tile_max[r], v);
+        }
+      }
+      float rescale[2], base[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float new_max = fmaxf(row_max[r], tile_max[r]);
+        base[r] = (new_max == -INFINITY) ? 0.0f : new_max;   // a row may see no key of an early tile
+        rescale[r] = exp2f(row_max[r] - base[r]);
+        row_max[r] = new_max;
+        row_sum[r] *= rescale[r];
+      }
+      unsigned pa[kKeys / 16][4];
+#pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j) {
+        const float p0 = exp2_approx(s_frag[j][0] - base[0]);
+        const float p1 = exp2_approx(s_frag[j][1] - base[0]);
+        const float p2 = exp2_approx(s_frag[j][2] - base[1]);
+        const float p3 = exp2_approx(s_frag[j][3] - base[1]);
+        row_sum[0] += p0 + p1;
+        row_sum[1] += p2 + p3;
+        pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int i = 0; i < kVD / 8; ++i) {
+        o[i][0] *= rescale[0];
+        o[i][1] *= rescale[0];
+        o[i][2] *= rescale[1];
+        o[i][3] *= rescale[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < kKeys / 16; ++kk) {
+#pragma unroll
+        for (int np = 0; np < kVD / 16; ++np) {
+          unsigned b[4];
+          const int row = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+          const int col = np * 16 + (lane >> 4) * 8;
+          ldmatrix_x4_trans(b, v_smem + (size_t)row * kVRow + col);
+          mma_bf16(o[np * 2], pa[kk], b[0], b[1]);
+          mma_bf16(o[np * 2 + 1], pa[kk], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // everyone is done with this stage before it is overwritten
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (my_row[r] >= rows_here) continue;
+    const float inv = 1.0f / row_sum[r];
+    const size_t row = (size_t)(row0 + my_row[r]);
+    __nv_bfloat16* dst = out + (row * heads + head) * kVD + 2 * t;
+    const __nv_bfloat16* gate = gate_offset >= 0 ? rows + row * row_stride + gate_offset + (size_t)head * kVD + 2 * t : nullptr;
+#pragma unroll
+    for (int i = 0; i < kVD / 8; ++i) {
+      float a = o[i][r * 2] * inv, b = o[i][r * 2 + 1] * inv;
+      if (gate != nullptr) {
+        const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(gate + i * 8);
+        a *= 1.0f / (1.0f + __expf(-__bfloat162float(gv.x)));
+        b *= 1.0f / (1.0f + __expf(-__bfloat162float(gv.y)));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(a, b);
+    }
+  }
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+TLIE_EXPORT int tlie_mixed_prefill_tile_rows() { return kRows; }
+TLIE_EXPORT int tlie_mixed_prefill_folded_width() { return kParts * kD; }
+
+// ``folded``: scratch for the folded queries, bfloat16 [tokens, heads, PARTS * KEY_DIM].  ``slopes``: the folded slopes (or null).
+// ``mix`` null: PARTS must be 1.  ``longest``: the most rows any entry of the step has.
+TLIE_EXPORT int tlie_mixed_prefill(const void* rows, int row_stride, int gate_offset, const float* mix, float scale, void* folded, const void* k_pages,
+                                   long long k_page_stride, const void* v_pages, long long v_page_stride, const int* seq_starts,
+                                   const int* first_positions, const int* block_table, int table_stride, const float* slopes, void* out, int tokens,
+                                   int entries, int longest, int heads, int kv_heads, int page_size, int window, cudaStream_t stream) {
+  if (tokens <= 0 || entries <= 0) return 0;
+  if (kRows == 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size % 16 != 0 || heads > 65535 || entries > 65535 ||
+      (mix != nullptr ? kParts != kv_heads : kParts != 1) || row_stride % 8 != 0 || (gate_offset >= 0 && gate_offset % 2 != 0))
+    return (int)cudaErrorInvalidValue;
+  fold_queries_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, mix, scale, (__nv_bfloat16*)folded, heads, heads / kv_heads);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  constexpr size_t smem = smem_for(kRows > 0 ? kRows : 16, kStages);
+  static bool configured = false;
+  if (!configured) {
+    e = cudaFuncSetAttribute(mixed_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tile_rows = kRows > 0 ? kRows : 16;
+  const dim3 grid((longest + tile_rows - 1) / tile_rows, entries, heads);
+  mixed_prefill_kernel<<<grid, kThreads, smem, stream>>>((const __nv_bfloat16*)folded, (const __nv_bfloat16*)rows, row_stride, gate_offset,
+                                                         (const __nv_bfloat16*)k_pages, k_page_stride, (const __nv_bfloat16*)v_pages, v_page_stride,
+                                                         seq_starts, first_positions, block_table, table_stride, slopes, (__nv_bfloat16*)out, heads,
+                                                         kv_heads, page_size, window, mix != nullptr ? 1 : 0);
+  return (int)cudaGetLastError();
+}

@@ -430,13 +430,15 @@ def store_kv_planes(rows, k_offset: int, v_offset: int, positions, token_seq, ca
 
 
 def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
-                          window: int, scale: float, batch=None) -> None:
+                          window: int, scale: float, batch=None, folded_slopes=None) -> None:
     """Attention over the paged keys with a distance bias, the heads' scores mixed before the softmax, and an output gate.
 
     ``rows`` [T, >= heads * key_dim]: each row starts with its query heads; ``gate_offset`` (>= 0) names the column where
     ``heads * value_dim`` gate pre-activations start (the output is multiplied by their sigmoid), -1 for none.  Score of query
     head g at position i for key j: (q . k) * scale - slopes[g] * (i - j) (``slopes`` 32-bit [heads] or None); head h then sees
-    sum_g mix[h, g] score_g (``mix`` 32-bit [heads, heads] or None); keys with 0 <= i - j (< window if window > 0) are visible."""
+    sum_g mix[h, g] score_g (``mix`` 32-bit [heads, heads] or None); keys with 0 <= i - j (< window if window > 0) are visible.
+    ``batch``: the step's context, from which a faster kernel is chosen where one fits; ``folded_slopes``: ``fast.folded_slopes(slopes, mix)``
+    if the caller keeps it (it is worked out here otherwise)."""
     tokens = rows.shape[0]
     if heads % kv_heads != 0 or out.shape != (tokens, heads * value_dim) or out.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: out must be [rows, heads * value_dim] of the rows' dtype, heads a multiple of kv heads", code="invalid_shape")
@@ -447,10 +449,22 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     if pages.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: pages and rows differ in dtype", code="invalid_dtype")
     table = cache.block_table
+    if rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset):
+        folded = folded_slopes if folded_slopes is not None else fast.folded_slopes(slopes, mix)
+        fast.mixed_prefill(rows, gate_offset, batch, table, (k_ptr, k_stride, v_ptr, v_stride), folded, mix, out, heads, kv_heads, key_dim, value_dim,
+                           cache.page_size, window, scale)
+        return
+    # few rows over long contexts (decode steps): every row's keys are dealt to several CTAs
+    splits, partial = 1, None
+    if batch is not None and tokens * 2 <= fast.sm_count():
+        reach = min(window, batch.max_seq_len) if window > 0 else batch.max_seq_len
+        splits = max(1, min(2 * fast.sm_count() // tokens, reach // 128, 64))
+        if splits > 1:
+            partial = fast.mixed_scratch(rows.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32)
     _check(mixed_attention().tlie_mixed_heads_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr,
                                                         c_longlong(v_stride), _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"),
                                                         c_int(table.shape[1]), _ptr(slopes), _ptr(mix), _ptr(out), c_int(tokens), c_int(heads), c_int(kv_heads),
-                                                        c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), _stream()),
+                                                        c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), c_int(splits), _ptr(partial), _stream()),
            "mixed_heads_attention")
 
 

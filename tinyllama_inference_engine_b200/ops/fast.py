@@ -670,5 +670,70 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
     return False
 
 
+# --- attention with mixed heads, prompt portions on the tensor cores -----------------------------------------------------------------
+use_mixed_prefill = True
+MIXED_PREFILL_MIN_ROWS = 8    # a step whose longest entry has fewer rows stays on the general kernel (a tile is at least 16 rows)
+
+
+def mixed_prefill_library(key_dim: int, value_dim: int, parts: int):
+    """The kernel set of one (key width, value width, key heads per folded query): compiled when a model of these sizes first runs a prompt."""
+    lib = load_library(f"tlie_attn_mixed_k{key_dim}_v{value_dim}_p{parts}", ["attention_mixed_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "PARTS": parts})
+    return lib
+
+
+def mixed_prefill_takes(batch, rows, page_size: int, parts: int, key_dim: int, value_dim: int, gate_offset: int) -> bool:
+    """Whether a step's attention with mixed heads runs on the tensor-core kernel: bfloat16, a prompt portion among the entries,
+    widths that are multiples of 16, and tiles that fit shared memory (the kernel set says how many rows its tile has: 0 = none)."""
+    if not use_mixed_prefill or batch is None or batch.max_q_len < MIXED_PREFILL_MIN_ROWS or rows.dtype != torch.bfloat16:
+        return False
+    if key_dim % 16 or value_dim % 16 or page_size % 16 or rows.shape[1] % 8 or (gate_offset >= 0 and gate_offset % 2) or batch.num_seqs > 65535:
+        return False
+    if ((parts * key_dim + 8) * 16 + parts * 64 * (key_dim + 8) + 64 * (value_dim + 8)) * 2 > 227 * 1024:
+        return False   # not even a tile of 16 rows with one stage fits
+    return mixed_prefill_library(key_dim, value_dim, parts).tlie_mixed_prefill_tile_rows() > 0
+
+
+def folded_slopes(slopes, mix):
+    """slope'_h = sum_g mix[h, g] slope_g: the distance bias of head h once the heads' scores are mixed.  A part works this out once
+    when it is built and hands it to every call."""
+    if slopes is None or mix is None:
+        return slopes
+    return (mix.view(slopes.numel(), -1).double() @ slopes.double()).float().contiguous()
+
+
+_mixed_scratch: dict[tuple, list] = {}
+
+
+def mixed_scratch(device: torch.device, elements: int, dtype: torch.dtype) -> torch.Tensor:
+    """Scratch of the attention kernels with mixed heads (folded queries, the parts of rows cut over several CTAs): buffers of
+    stable address, grown by adding a larger one and never freed, since a captured graph may still point at an earlier one.  Apart
+    from ``scratch``, whose first words the split-key decode kernel keeps as counters."""
+    held = _mixed_scratch.setdefault((device, dtype), [])
+    if not held or held[-1].numel() < elements:
+        held.append(torch.empty(max(elements, 1 << 20), dtype=dtype, device=device))
+    return held[-1]
+
+
+def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                  page_size: int, window: int, scale: float) -> None:
+    """Attention with mixed heads for a step that carries prompt portions (csrc/attention_mixed_prefill.cu): the mix is folded into
+    the queries by a first kernel, the second is flash attention over the concatenated key heads.  ``planes``: (key plane pointer,
+    its page stride in elements, value plane pointer, its page stride); ``folded``: the folded slopes (``folded_slopes``) or None."""
+    ops = _ops()
+    parts = kv_heads if mix is not None else 1
+    tokens = rows.shape[0]
+    need = tokens * heads * parts * key_dim
+    held = mixed_scratch(rows.device, need, torch.bfloat16)
+    k_ptr, k_stride, v_ptr, v_stride = planes
+    ops._check(
+        mixed_prefill_library(key_dim, value_dim, parts).tlie_mixed_prefill(
+            ops._ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), ops._ptr(mix), c_float(scale), ops._ptr(held), k_ptr, c_longlong(k_stride), v_ptr,
+            c_longlong(v_stride), ops._i32(batch.seq_starts, "seq_starts"), ops._i32(batch.first_positions, "first_positions"), ops._i32(block_table, "block_table"),
+            c_int(block_table.shape[1]), ops._ptr(folded), ops._ptr(out), c_int(tokens), c_int(batch.num_seqs), c_int(batch.max_q_len),
+            c_int(heads), c_int(kv_heads), c_int(page_size), c_int(window), ops._stream()),
+        "mixed_prefill")
+    ops.launch_count += 1   # two kernels: the fold and the attention
+
+
 if os.environ.get("TLIE_SKINNY", "0") == "1":
     enable_skinny(True)

@@ -147,6 +147,7 @@ class MixedHeadsAttention(Mixer):
         slopes = spec.get("distance_slopes")
         self.slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32, device=runtime.device)
         self.mix = weights.get(f"{prefix}.talk", torch.float32).contiguous() if spec.get("mix_heads") else None
+        self.folded_slopes = ops.fast.folded_slopes(self.slopes, self.mix) if self.slopes is not None and self.slopes.is_cuda else None
 
     def adds_to_residual(self, rows: int) -> bool:
         return ops.can_accumulate(rows, self.w_o)
@@ -162,7 +163,7 @@ class MixedHeadsAttention(Mixer):
             ops.store_kv_planes(rows, self.k_offset, self.v_offset, ctx.positions, ctx.token_seq, cache, self.kv_heads, self.key_dim, self.value_dim)
         mixed = ws.get("attention", tokens, self.heads * self.value_dim, dtype)
         ops.mixed_heads_attention(rows, self.gate_offset, ctx.positions, ctx.token_seq, cache, self.slopes, self.mix, mixed, self.heads, self.kv_heads,
-                                  self.key_dim, self.value_dim, self.window, self.scale, batch=ctx)
+                                  self.key_dim, self.value_dim, self.window, self.scale, batch=ctx, folded_slopes=self.folded_slopes)
         if accumulate_into is not None:
             ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
             return None
