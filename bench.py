@@ -341,6 +341,185 @@ def run_engine(args) -> dict:
     }
 
 
+# --- another design beside the closest existing one ---------------------------------------------------------------------------
+# `--designs`: Marutar (minGRU layers and attention with mixed heads, a sliding window and an output gate) at sizes that resemble
+# real models' layers, beside the Llama decoder at equal width, heads, feed-forward and layer count: prompt and decode throughput
+# through the same engine, and the design's own kernels alone beside the like kernels of the Llama path, each against its roofline.
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, recurrent=2048, heads=32, kv_heads=4, dim=64, vdim=64, window=1024, ff=5632, vocab=32000, positions=4096, layers=8,
+                  pattern=("mingru", "mingru", "attention", "mingru")),
+    "w4096": dict(width=4096, recurrent=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=2048, ff=14336, vocab=32000, positions=4096, layers=4,
+                  pattern=("mingru", "attention")),
+}
+
+
+def design_configs(size: dict) -> tuple[dict, dict]:
+    """config.json of the Marutar model and of the Llama model of equal width, heads, feed-forward and layer count."""
+    layers = []
+    for index in range(size["layers"]):
+        kind = size["pattern"][index % len(size["pattern"])]
+        if kind == "mingru":
+            layers.append({"type": "mingru", "mixer": {"width": size["recurrent"]}, "mlp": {"kind": "dense", "ff": size["ff"]}})
+        else:
+            layers.append({"type": "attention", "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"],
+                                                          "scale": size["dim"] ** -0.5, "mask": {"size": size["window"]}}, "mlp": {"kind": "dense", "ff": size["ff"]}})
+    marutar = {"architecture": "Marutar", "vocab": size["vocab"], "width": size["width"], "max_positions": size["positions"], "norm": {"eps": 1e-5}, "layers": layers}
+    llama = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=size["layers"],
+                 num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"], max_position_embeddings=size["positions"],
+                 vocab_size=size["vocab"], rms_norm_eps=1e-5, rope_theta=10000.0, bos_token_id=1, eos_token_id=2)
+    return marutar, llama
+
+
+def run_designs(args) -> dict:
+    import numpy as np
+    import torch
+
+    from tinyllama_inference_engine_b200 import EngineConfig, ops
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry, pack_step
+    from tinyllama_inference_engine_b200.engine.decode_session import DecodeSession
+    from tinyllama_inference_engine_b200.engine.request import SamplingParams
+    from tinyllama_inference_engine_b200.engine.runner import ModelRunner
+    from tinyllama_inference_engine_b200.ops import fast
+    from tinyllama_inference_engine_b200.parts.base import CacheNeed, LayerCache
+    from tinyllama_inference_engine_b200.weights import write_random_model
+
+    peak, peak_kind = peaks()
+    device = torch.device("cuda:0")
+    rng = np.random.default_rng(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)   # larger than L2: written between timed launches
+    prompt_tokens, context, batch, steps = 2048, 1024, args.batch, min(args.steps, 64)
+
+    def timed(fn, repeats=7) -> float:
+        """Median device time (ms) of ``fn`` alone, L2 flushed before every launch."""
+        times = []
+        for index in range(3 + repeats):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            if index >= 3:
+                times.append(start.elapsed_time(end))
+        return sorted(times)[len(times) // 2]
+
+    def model_numbers(folder) -> dict:
+        runner = ModelRunner(folder, EngineConfig(dtype="bfloat16", page_size=64, max_cache_tokens=batch * (context + 256) + prompt_tokens + 64, max_requests=batch + 1,
+                                                  max_batch_tokens=prompt_tokens))
+        vocab = runner.spec.vocab_size
+        prompt_ms = []
+        for index in range(8):   # the shape repeats: from its second use on the step is a replayed graph, for both designs alike
+            tokens = [int(t) for t in rng.integers(0, vocab, size=prompt_tokens)]
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(f"p{index}", tokens, [prompt_tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            prompt_ms.append(start.elapsed_time(end))
+            runner.finish(f"p{index}")
+        prefill = sorted(prompt_ms[3:])[len(prompt_ms[3:]) // 2]
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, vocab, size=context)], [])])
+        session = DecodeSession(runner, batch, publish=False)
+        session.load(ids, [int(t) for t in rng.integers(0, vocab, size=batch)], [SamplingParams()] * batch, [0] * batch)
+        for _ in range(4):
+            session.step()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            session.step()
+        end.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(end) / steps
+        weights = sum(t.numel() * t.element_size() for part in [runner.model.embedding, *runner.model.blocks, runner.model.head] for t in _tensors_of(part))
+        out = {"prefill_ms": prefill, "prefill_tokens_per_s": prompt_tokens / (prefill / 1e3), "decode_ms_per_step": decode_ms, "decode_tokens_per_s": batch / (decode_ms / 1e3),
+               "weight_bytes": weights, "decode_hbm_frac": weights / (decode_ms / 1e3) / 1e9 / peak["hbm_gbs"], "kernels_per_decode_step": session.kernels_per_step,
+               "library_gemms_per_decode_step": session.library_calls_per_step}
+        del session, runner
+        torch.cuda.empty_cache()
+        return out
+
+    def _tensors_of(part, seen=None):
+        seen = set() if seen is None else seen
+        for value in vars(part).values():
+            if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                seen.add(value.data_ptr())
+                yield value
+            elif hasattr(value, "runtime") and hasattr(value, "spec"):
+                yield from _tensors_of(value, seen)
+
+    def kernel_numbers(size: dict) -> dict:
+        """The design's own kernels alone, and the Llama path's attention kernels at the same heads, widths and window."""
+        H, G, D, VD, W, R = size["heads"], size["kv_heads"], size["dim"], size["vdim"], size["window"], size["recurrent"]
+        page, bf16 = 64, torch.bfloat16
+        out = {}
+        pages_needed = -(-(context + 1) // page) * batch + -(-prompt_tokens // page)
+        pages = torch.randn(pages_needed, 2, G, page, D, dtype=torch.float32, device=device).to(bf16)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32, device=device)
+        mix = (torch.randn(H, H, device=device) * H ** -0.5).contiguous()
+        folded = fast.folded_slopes(slopes, mix)
+
+        def context_for(lens, firsts):
+            table_width = size["positions"] // page
+            rows, at = [], 0
+            for n, f in zip(lens, firsts):
+                count = -(-(f + n) // page)
+                rows.append(list(range(at, at + count)) + [-1] * (table_width - count))
+                at += count
+            entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lens)]
+            return pack_step(entries, list(firsts), list(range(len(lens))), [rows], device)
+
+        for name, lens, firsts in (("prefill", [prompt_tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            ctx = context_for(lens, firsts)
+            tokens = sum(lens)
+            cache = LayerCache(CacheNeed("pages"), True, pages, ctx.block_tables[0], page)
+            visible = sum(min(f + i + 1, W) for n, f in zip(lens, firsts) for i in range(n))
+            rows = torch.randn(tokens, H * D + G * D + G * VD + H * VD, device=device).to(bf16)
+            mixed = torch.empty(tokens, H * VD, dtype=bf16, device=device)
+            ms = timed(lambda: ops.mixed_heads_attention(rows, H * D + G * D + G * VD, ctx.positions, ctx.token_seq, cache, slopes, mix, mixed, H, G, D, VD, W, D ** -0.5,
+                                                         batch=ctx, folded_slopes=folded))
+            qkv = torch.randn(tokens, (H + 2 * G) * D, device=device).to(bf16)
+            plain = torch.empty(tokens, H * D, dtype=bf16, device=device)
+            like_ms = timed(lambda: ops.paged_attention(qkv, pages, ctx.positions, ctx.token_seq, ctx.block_tables[0], plain, H, G, D, page, W, D ** -0.5, batch=ctx))
+            if name == "prefill":
+                flops, like_flops = visible * H * (2.0 * (D + VD) + 2.0 * H), visible * H * 4.0 * D
+                out["attention_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+                                            "like_ms": like_ms, "like_tflops": like_flops / like_ms / 1e9, "like_frac": like_flops / (like_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+            else:
+                moved = visible * G * (D + VD) * 2.0
+                out["attention_decode"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                           "like_ms": like_ms, "like_gbs": moved / like_ms / 1e6, "like_frac": moved / (like_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            zxg = torch.randn(tokens, 3 * R, device=device).to(bf16)
+            gated = torch.empty(tokens, R, dtype=bf16, device=device)
+            state = torch.zeros(batch + 1, R, device=device)
+            bias = torch.zeros(R, device=device)
+            scan_ms = timed(lambda: ops.mingru_scan(zxg, bias, bias, state, ctx.seq_starts, ctx.state_slots, gated, max(lens)))
+            moved = tokens * 4.0 * R * 2 + (len(lens) * R * 8 if name == "decode" else 0)
+            out[f"mingru_scan_{name}"] = {"ms": scan_ms, "gbs": moved / scan_ms / 1e6, "frac": moved / (scan_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+        return out
+
+    results = {}
+    with ClockSampler() as clocks:
+        for key, size in DESIGN_SIZES.items():
+            marutar, llama = design_configs(size)
+            base = Path(tempfile.gettempdir()) / f"tlie_b200_designs_{os.getuid()}_{key}"
+            folders = {}
+            for name, config in (("marutar", marutar), ("llama", llama)):
+                folders[name] = base / name
+                if not (folders[name] / "model.safetensors").exists():
+                    write_random_model(folders[name], config, seed=0)
+            results[key] = {"marutar": model_numbers(folders["marutar"]), "llama": model_numbers(folders["llama"]), "kernels": kernel_numbers(size),
+                            "sizes": {k: v for k, v in size.items() if k != "pattern"} | {"pattern": "/".join(size["pattern"])}}
+    return {"metric": "prompt and decode throughput of Marutar beside the Llama decoder at equal sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic (random weights, uniform random token ids)", "impl": "engine", "higher_is_better": True,
+            "config": {"prompt_tokens": prompt_tokens, "decode_context": context, "decode_batch": batch, "decode_steps": steps, "page_size": 64, "peaks": peak_kind,
+                       "l2": "a buffer larger than L2 is written before every timed launch"},
+            "peaks": peak, "designs": results, "clocks": clocks.summary()}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference on the same metric: TinyLlama 1.1B, 1,024-token prompts, greedy decoding, float16."""
     sys.path.insert(0, str(ROOT / "baseline"))
@@ -394,10 +573,15 @@ def main() -> int:
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
     parser.add_argument("--sections", default="decode,e2e,prefill,points,mixed", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
+    parser.add_argument("--designs", action="store_true", help="instead of the headline workload: Marutar beside the Llama decoder at equal sizes (prompt and decode "
+                                                               "throughput through the engine, and the design's own kernels against their rooflines)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")
         return 2
+    if args.designs:
+        print(json.dumps(run_designs(args)))
+        return 0
     print(json.dumps(run_reference(args) if args.impl == "reference" else run_engine(args)))
     return 0
 

@@ -78,12 +78,66 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const __nv
   return dot;
 }
 
+// A tile's rows of one plane (``heads`` x ``count`` rows of ``width``) from their pages into shared memory, rows ``stride`` apart.
+// 16 bytes per load where the width allows it: all of a thread's loads are in flight together.
+template <typename T>
+__device__ __forceinline__ void stage_plane(T* __restrict__ dst, int stride, const T* __restrict__ pages, const long long* __restrict__ row_at,
+                                            int head_stride, int heads, int count, int width) {
+  constexpr int kVec = 16 / sizeof(T);
+  if (width % kVec == 0) {
+    const int chunks = width / kVec;
+    for (int i = threadIdx.x; i < heads * kMixKeys * chunks; i += kMixThreads) {
+      const int chunk = i % chunks, j = (i / chunks) % kMixKeys, c = i / (chunks * kMixKeys);
+      if (j >= count) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(pages + row_at[j] + (size_t)c * head_stride + chunk * kVec);
+      unsigned* out = reinterpret_cast<unsigned*>(dst + (size_t)(c * kMixKeys + j) * stride + chunk * kVec);   // rows are 4-byte aligned, not 16
+      out[0] = raw.x;
+      out[1] = raw.y;
+      out[2] = raw.z;
+      out[3] = raw.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < heads * kMixKeys * width; i += kMixThreads) {
+      const int d = i % width, j = (i / width) % kMixKeys, c = i / (width * kMixKeys);
+      if (j < count) dst[(size_t)(c * kMixKeys + j) * stride + d] = pages[row_at[j] + (size_t)c * head_stride + d];
+    }
+  }
+}
+
+__device__ __forceinline__ float dot_staged(const float* __restrict__ q, const float* __restrict__ k, int n) {
+  float dot = 0.0f;
+  for (int d = 0; d < n; ++d) dot += q[d] * k[d];
+  return dot;
+}
+
+__device__ __forceinline__ float dot_staged(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int n) {
+  float dot = 0.0f;
+  if ((n & 1) == 0) {
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(k);
+    for (int d = 0; d < n / 2; ++d) {
+      const float2 kv = __bfloat1622float2(pairs[d]);
+      dot += q[2 * d] * kv.x;
+      dot += q[2 * d + 1] * kv.y;
+    }
+  } else {
+    for (int d = 0; d < n; ++d) dot += q[d] * __bfloat162float(k[d]);
+  }
+  return dot;
+}
+
+// Shared-memory row stride of a staged key tile: lanes read different rows at the same column, so rows are an odd number of
+// 4-byte words apart where the width allows it.
+template <typename T>
+__host__ __device__ constexpr int staged_key_stride(int key_dim) {
+  return sizeof(T) == 4 ? key_dim + 1 : ((key_dim & 1) ? key_dim + 1 : (((key_dim / 2) & 1) ? key_dim : key_dim + 2));
+}
+
 template <typename T, int ACC>
 __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     const T* __restrict__ rows, int row_stride, int gate_offset, const T* __restrict__ k_pages, long long k_page_stride,
     const T* __restrict__ v_pages, long long v_page_stride, const int* __restrict__ positions, const int* __restrict__ token_seq,
     const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, const float* __restrict__ mix, T* __restrict__ out,
-    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale, float* __restrict__ partial) {
+    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale, float* __restrict__ partial, int staged) {
   extern __shared__ __align__(16) unsigned char smem_bytes[];
   long long* k_at = reinterpret_cast<long long*>(smem_bytes);   // [32] where a key's row starts in its plane (head 0)
   long long* v_at = k_at + kMixKeys;
@@ -94,6 +148,11 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
   float* max_s = p_s + heads * kMixKeys;         // [heads] running maximum
   float* sum_s = max_s + heads;                  // [heads] running sum
   float* rescale_s = sum_s + heads;              // [heads] what this tile shrinks the sums so far by
+  // ``staged``: the tile's keys and values of every key/value head pass through shared memory (wide loads, all in flight at once,
+  // every row read from memory once however many heads share it); sizes too large for that read their rows from global memory.
+  const int k_stride = staged_key_stride<T>(key_dim);
+  T* k_t = reinterpret_cast<T*>(smem_bytes + (((size_t)((rescale_s + heads) - reinterpret_cast<float*>(smem_bytes)) * sizeof(float)) + 15) / 16 * 16);
+  T* v_t = k_t + (size_t)kv_heads * kMixKeys * k_stride;   // [kv heads][32][value_dim]; k_t is [kv heads][32][k_stride]
 
   const int t = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -113,13 +172,14 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
   }
 
   float acc[ACC];
-  int head_of[ACC], value_at[ACC];   // the output's head, and where its element lies inside a token's value plane entry
+  int head_of[ACC], value_at[ACC], staged_at[ACC];   // the output's head, and where its element lies in a token's value plane entry / in the staged tile
 #pragma unroll
   for (int i = 0; i < ACC; ++i) {
     const int o = tid + i * kMixThreads;
     acc[i] = 0.0f;
     head_of[i] = o < outputs ? o / value_dim : 0;
     value_at[i] = (head_of[i] / group) * page_size * value_dim + (o - head_of[i] * value_dim);
+    staged_at[i] = (head_of[i] / group) * kMixKeys * value_dim + (o - head_of[i] * value_dim);
   }
 
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -141,12 +201,19 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
       v_at[tid] = page * v_page_stride + (long long)slot * value_dim;
     }
     __syncthreads();
+    if (staged) {
+      stage_plane(k_t, k_stride, k_pages, k_at, page_size * key_dim, kv_heads, count, key_dim);
+      stage_plane(v_t, value_dim, v_pages, v_at, page_size * value_dim, kv_heads, count, value_dim);
+      __syncthreads();
+    }
     // raw scores: a warp per head, a lane per key
     for (int g = warp; g < heads; g += warps) {
       float raw = 0.0f;
       if (lane < count) {
-        const T* k_row = k_pages + k_at[lane] + (size_t)(g / group) * page_size * key_dim;
-        raw = dot_row(q_s + g * key_dim, k_row, key_dim) * scale;
+        if (staged)
+          raw = dot_staged(q_s + g * key_dim, k_t + (size_t)((g / group) * kMixKeys + lane) * k_stride, key_dim) * scale;
+        else
+          raw = dot_row(q_s + g * key_dim, k_pages + k_at[lane] + (size_t)(g / group) * page_size * key_dim, key_dim) * scale;
         if (slopes) raw -= slopes[g] * (float)(pos - (base + lane));
       }
       raw_s[g * kMixKeys + lane] = raw;
@@ -179,11 +246,19 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     // weights times values: every thread its share of the outputs
 #pragma unroll
     for (int i = 0; i < ACC; ++i) acc[i] *= rescale_s[head_of[i]];
-    for (int j = 0; j < count; ++j) {
-      const T* v_row = v_pages + v_at[j];
+    if (staged) {
+      for (int j = 0; j < count; ++j) {
 #pragma unroll
-      for (int i = 0; i < ACC; ++i)
-        if (tid + i * kMixThreads < outputs) acc[i] += p_s[head_of[i] * kMixKeys + j] * to_float(v_row[value_at[i]]);
+        for (int i = 0; i < ACC; ++i)
+          if (tid + i * kMixThreads < outputs) acc[i] += p_s[head_of[i] * kMixKeys + j] * to_float(v_t[staged_at[i] + j * value_dim]);
+      }
+    } else {
+      for (int j = 0; j < count; ++j) {
+        const T* v_row = v_pages + v_at[j];
+#pragma unroll
+        for (int i = 0; i < ACC; ++i)
+          if (tid + i * kMixThreads < outputs) acc[i] += p_s[head_of[i] * kMixKeys + j] * to_float(v_row[value_at[i]]);
+      }
     }
   }
   __syncthreads();
@@ -247,13 +322,18 @@ static int launch_mixed(const void* rows, int row_stride, int gate_offset, const
                         const float* slopes, const float* mix, void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
                         int page_size, int window, float scale, size_t smem, int splits, float* partial, cudaStream_t stream) {
   auto kernel = mixed_heads_attention_kernel<T, ACC>;
+  // room for a tile's keys and values of every key/value head behind the 32-bit part; without it rows are read from global memory
+  const size_t tiles = (size_t)kv_heads * kMixKeys * ((size_t)staged_key_stride<T>(key_dim) + value_dim) * sizeof(T);
+  const size_t with_tiles = (smem + 15) / 16 * 16 + tiles;
+  const int staged = with_tiles <= 160 * 1024 ? 1 : 0;
+  if (staged) smem = with_tiles;
   if (smem > 48 * 1024) {
     const cudaError_t set = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (set != cudaSuccess) return (int)set;
   }
   kernel<<<dim3(tokens, splits), kMixThreads, smem, stream>>>((const T*)rows, row_stride, gate_offset, (const T*)k_pages, k_page_stride, (const T*)v_pages,
                                                               v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
-                                                              kv_heads, key_dim, value_dim, page_size, window, scale, partial);
+                                                              kv_heads, key_dim, value_dim, page_size, window, scale, partial, staged);
   if (splits > 1)
     merge_mixed_kernel<T><<<tokens, 256, 0, stream>>>(partial, (const T*)rows, row_stride, gate_offset, (T*)out, heads, value_dim, splits);
   return (int)cudaGetLastError();

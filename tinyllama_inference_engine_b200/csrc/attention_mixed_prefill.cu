@@ -38,8 +38,8 @@ constexpr size_t smem_for(int rows, int stages) {
 }
 constexpr bool fits(int rows, int stages) { return smem_for(rows, stages) <= kSmemLimit; }
 // rows per CTA and stages: the largest that fits shared memory; 0 rows if nothing does (the host then uses the general kernel)
-constexpr int kRows = fits(64, 2) ? 64 : fits(32, 2) ? 32 : fits(64, 1) ? 64 : fits(32, 1) ? 32 : fits(16, 1) ? 16 : 0;
-constexpr int kStages = (fits(64, 2) || fits(32, 2)) ? 2 : 1;
+constexpr int kRows = fits(128, 2) ? 128 : fits(64, 2) ? 64 : fits(32, 2) ? 32 : fits(64, 1) ? 64 : fits(32, 1) ? 32 : fits(16, 1) ? 16 : 0;
+constexpr int kStages = (fits(128, 2) || fits(64, 2) || fits(32, 2)) ? 2 : 1;
 constexpr int kWarps = kRows > 0 ? kRows / 16 : 1;
 constexpr int kThreads = kWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;

@@ -24,10 +24,12 @@ struct GateStep {
 
 __device__ __forceinline__ float sigmoidf(float v) { return 1.0f / (1.0f + expf(-v)); }
 
-template <typename T>
-__device__ __forceinline__ GateStep mingru_gate(const T* __restrict__ row, int width, int c, float bias_z, float bias_x) {
-  const float z = sigmoidf(to_float(row[c]) + bias_z);
-  const float u = to_float(row[width + c]) + bias_x;
+constexpr int kScanBatch = 8;   // rows whose loads a thread has in flight together
+
+// one token's update from its two pre-activations: z = sigmoid(a + bias_z), candidate from x + bias_x
+__device__ __forceinline__ GateStep mingru_step(float a, float x, float bias_z, float bias_x) {
+  const float z = sigmoidf(a + bias_z);
+  const float u = x + bias_x;
   const float cand = u >= 0.0f ? u + 0.5f : sigmoidf(u);
   return {1.0f - z, z * cand};
 }
@@ -52,10 +54,22 @@ __global__ void __launch_bounds__(kScanChannels* kScanMaxRuns) mingru_scan_kerne
   if (runs > 1) {
     float keep = 1.0f, drive = 0.0f;
     if (live)
-      for (int t = lo; t < hi; ++t) {
-        const GateStep g = mingru_gate(zxg + (size_t)(first + t) * stride, width, c, bz, bx);
-        keep *= g.keep;
-        drive = g.keep * drive + g.drive;
+      for (int t0 = lo; t0 < hi; t0 += kScanBatch) {
+        // a batch of rows' loads are issued together; the updates then run in order
+        float a[kScanBatch], u[kScanBatch];
+#pragma unroll
+        for (int k = 0; k < kScanBatch; ++k) {
+          const T* row = zxg + (size_t)(first + min(t0 + k, hi - 1)) * stride;
+          a[k] = to_float(row[c]);
+          u[k] = to_float(row[width + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < kScanBatch; ++k) {
+          if (t0 + k >= hi) break;
+          const GateStep g = mingru_step(a[k], u[k], bz, bx);
+          keep *= g.keep;
+          drive = g.keep * drive + g.drive;
+        }
       }
     keep_of[run][threadIdx.x] = keep;
     drive_of[run][threadIdx.x] = drive;
@@ -72,12 +86,22 @@ __global__ void __launch_bounds__(kScanChannels* kScanMaxRuns) mingru_scan_kerne
   }
   if (!live) return;
   float s = runs > 1 ? start_of[run][threadIdx.x] : slot[c];
-  for (int t = lo; t < hi; ++t) {
-    const T* row = zxg + (size_t)(first + t) * stride;
-    const GateStep g = mingru_gate(row, width, c, bz, bx);
-    s = g.keep * s + g.drive;
-    const float gate = to_float(row[2 * width + c]);
-    out[(size_t)(first + t) * width + c] = from_float<T>(s * (gate * sigmoidf(gate)));
+  for (int t0 = lo; t0 < hi; t0 += kScanBatch) {
+    float a[kScanBatch], u[kScanBatch], gate[kScanBatch];
+#pragma unroll
+    for (int k = 0; k < kScanBatch; ++k) {
+      const T* row = zxg + (size_t)(first + min(t0 + k, hi - 1)) * stride;
+      a[k] = to_float(row[c]);
+      u[k] = to_float(row[width + c]);
+      gate[k] = to_float(row[2 * width + c]);
+    }
+#pragma unroll
+    for (int k = 0; k < kScanBatch; ++k) {
+      if (t0 + k >= hi) break;
+      const GateStep g = mingru_step(a[k], u[k], bz, bx);
+      s = g.keep * s + g.drive;
+      out[(size_t)(first + t0 + k) * width + c] = from_float<T>(s * (gate[k] * sigmoidf(gate[k])));
+    }
   }
   if (runs == 1) slot[c] = s;
 }

@@ -26,6 +26,7 @@ def sm_count() -> int:
     return 148
 
 DEFAULT_HEAD_DIMS = (64, 128)
+DEFAULT_MIXED_PREFILL_SETS = ((64, 64, 4), (128, 128, 8))   # (key width, value width, key heads per folded query) built ahead; others on first use
 _scratch: dict[torch.device, list[torch.Tensor]] = {}
 
 
@@ -38,6 +39,8 @@ def build_all() -> list:
     built.append(build_library("tlie_gemm_tcgen05", TCGEN05_SOURCES))
     built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
     built.append(build_library("tlie_probes", ["probes.cu"]))
+    for key_dim, value_dim, parts in DEFAULT_MIXED_PREFILL_SETS:
+        built.append(build_library(f"tlie_attn_mixed_k{key_dim}_v{value_dim}_p{parts}", ["attention_mixed_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "PARTS": parts}))
     return built
 
 
