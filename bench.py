@@ -386,7 +386,7 @@ def run_designs(args) -> dict:
     peak, peak_kind = peaks()
     device = torch.device("cuda:0")
     rng = np.random.default_rng(0)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)   # larger than L2: written between timed launches
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=device)   # larger than L2, written before every timed launch; long enough a write that the host has the launch queued when it ends
     prompt_tokens, context, batch, steps = 2048, 1024, args.batch, min(args.steps, 64)
 
     def timed(fn, repeats=7) -> float:

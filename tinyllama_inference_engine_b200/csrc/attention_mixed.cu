@@ -246,7 +246,13 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     // weights times values: every thread its share of the outputs
 #pragma unroll
     for (int i = 0; i < ACC; ++i) acc[i] *= rescale_s[head_of[i]];
-    if (staged) {
+    if (staged && outputs == ACC * kMixThreads) {   // every accumulator is in use: no guards
+#pragma unroll 2
+      for (int j = 0; j < count; ++j) {
+#pragma unroll
+        for (int i = 0; i < ACC; ++i) acc[i] += p_s[head_of[i] * kMixKeys + j] * to_float(v_t[staged_at[i] + j * value_dim]);
+      }
+    } else if (staged) {
       for (int j = 0; j < count; ++j) {
 #pragma unroll
         for (int i = 0; i < ACC; ++i)
@@ -289,20 +295,23 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
   }
 }
 
-// The parts of a row put together: out = sum_s acc_s e^(max_s - max) / sum_s total_s e^(max_s - max), then the gate.
+// The parts of a row put together: out = sum_s acc_s e^(max_s - max) / sum_s total_s e^(max_s - max), then the gate.  A CTA per
+// (row, head), a thread per output element: its loads over the parts do not depend on one another.
 template <typename T>
 __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* __restrict__ rows, int row_stride, int gate_offset, T* __restrict__ out,
                                    int heads, int value_dim, int splits) {
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int outputs = heads * value_dim;
-  const float* mine = partial + (size_t)t * splits * (outputs + 2 * heads);
-  for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
-    const int h = o / value_dim;
-    float highest = -INFINITY;
-    for (int s = 0; s < splits; ++s) highest = fmaxf(highest, mine[(size_t)s * (outputs + 2 * heads) + outputs + h]);
+  const size_t part_size = (size_t)outputs + 2 * heads;
+  const float* mine = partial + (size_t)t * splits * part_size;
+  float highest = -INFINITY;
+  for (int s = 0; s < splits; ++s) highest = fmaxf(highest, mine[s * part_size + outputs + h]);
+  for (int d = threadIdx.x; d < value_dim; d += blockDim.x) {
+    const int o = h * value_dim + d;
     float value = 0.0f, total = 0.0f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
-      const float* part = mine + (size_t)s * (outputs + 2 * heads);
+      const float* part = mine + s * part_size;
       const float weight = expf(part[outputs + h] - highest);   // a part that saw no key has maximum -inf: weight 0
       value += part[o] * weight;
       total += part[outputs + heads + h] * weight;
@@ -335,7 +344,8 @@ static int launch_mixed(const void* rows, int row_stride, int gate_offset, const
                                                               v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
                                                               kv_heads, key_dim, value_dim, page_size, window, scale, partial, staged);
   if (splits > 1)
-    merge_mixed_kernel<T><<<tokens, 256, 0, stream>>>(partial, (const T*)rows, row_stride, gate_offset, (T*)out, heads, value_dim, splits);
+    merge_mixed_kernel<T><<<dim3(tokens, heads), value_dim >= 128 ? 128 : (value_dim > 32 ? 64 : 32), 0, stream>>>(partial, (const T*)rows, row_stride, gate_offset,
+                                                                                                                  (T*)out, heads, value_dim, splits);
   return (int)cudaGetLastError();
 }
 
@@ -379,10 +389,12 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
                               table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, splits, partial, stream)
   if (dtype == TLIE_F32) {
     if (outputs <= 4 * kMixThreads) TLIE_MIXED(float, 4);
+    if (outputs <= 8 * kMixThreads) TLIE_MIXED(float, 8);
     if (outputs <= 16 * kMixThreads) TLIE_MIXED(float, 16);
     TLIE_MIXED(float, 32);
   }
   if (outputs <= 4 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 4);
+  if (outputs <= 8 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 8);
   if (outputs <= 16 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 16);
   TLIE_MIXED(__nv_bfloat16, 32);
 #undef TLIE_MIXED

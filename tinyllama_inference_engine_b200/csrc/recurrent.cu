@@ -7,7 +7,7 @@
 // in the request's state slot [slots, W].  Everything after the product is 32-bit.
 //
 // The recurrence is linear in S, S_t = p_t S_{t-1} + r_t, so a run of rows composes to S_end = P S_in + R.  A prompt portion
-// is cut into up to 32 runs per request: a thread per (run, channel) first finds its run's (P, R), one warp carries the state
+// is cut into up to 64 runs per request: a thread per (run, channel) first finds its run's (P, R), one warp carries the state
 // through the runs, and every thread walks its run again from the state it starts in, writing the outputs.  A single decoded
 // token is one run: read the state, one update, write it back.  How a request's rows were cut into steps and runs changes a
 // state only by rounding.
@@ -15,8 +15,8 @@
 
 namespace tlie {
 
-constexpr int kScanChannels = 32;   // channels per CTA: one warp's width, consecutive in memory
-constexpr int kScanMaxRuns = 32;
+constexpr int kScanChannels = 32;   // channels per CTA at most: one warp's width, consecutive in memory (16 where that fills more SMs)
+constexpr int kScanThreads = 1024;  // channels x runs of a CTA at most
 
 struct GateStep {
   float keep, drive;   // S <- keep * S + drive
@@ -35,12 +35,13 @@ __device__ __forceinline__ GateStep mingru_step(float a, float x, float bias_z, 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kScanChannels* kScanMaxRuns) mingru_scan_kernel(const T* __restrict__ zxg, const float* __restrict__ bias_z,
+__global__ void __launch_bounds__(kScanThreads) mingru_scan_kernel(const T* __restrict__ zxg, const float* __restrict__ bias_z,
                                                                                   const float* __restrict__ bias_x, float* __restrict__ state,
                                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
                                                                                   T* __restrict__ out, int width) {
-  __shared__ float keep_of[kScanMaxRuns][kScanChannels], drive_of[kScanMaxRuns][kScanChannels], start_of[kScanMaxRuns][kScanChannels];
-  const int c = blockIdx.x * kScanChannels + threadIdx.x;
+  __shared__ float keep_of[kScanThreads], drive_of[kScanThreads], start_of[kScanThreads];   // [run][channel of the CTA]
+  const int channels = blockDim.x;
+  const int c = blockIdx.x * channels + threadIdx.x;
   const int entry = blockIdx.y;
   const int runs = blockDim.y, run = threadIdx.y;
   const int first = seq_starts[entry], rows = seq_starts[entry + 1] - first;
@@ -71,21 +72,21 @@ __global__ void __launch_bounds__(kScanChannels* kScanMaxRuns) mingru_scan_kerne
           drive = g.keep * drive + g.drive;
         }
       }
-    keep_of[run][threadIdx.x] = keep;
-    drive_of[run][threadIdx.x] = drive;
+    keep_of[run * channels + threadIdx.x] = keep;
+    drive_of[run * channels + threadIdx.x] = drive;
     __syncthreads();
     if (run == 0 && live) {
       float s = slot[c];
       for (int r = 0; r < runs; ++r) {
-        start_of[r][threadIdx.x] = s;
-        s = keep_of[r][threadIdx.x] * s + drive_of[r][threadIdx.x];
+        start_of[r * channels + threadIdx.x] = s;
+        s = keep_of[r * channels + threadIdx.x] * s + drive_of[r * channels + threadIdx.x];
       }
       slot[c] = s;
     }
     __syncthreads();
   }
   if (!live) return;
-  float s = runs > 1 ? start_of[run][threadIdx.x] : slot[c];
+  float s = runs > 1 ? start_of[run * channels + threadIdx.x] : slot[c];
   for (int t0 = lo; t0 < hi; t0 += kScanBatch) {
     float a[kScanBatch], u[kScanBatch], gate[kScanBatch];
 #pragma unroll
@@ -110,12 +111,16 @@ __global__ void __launch_bounds__(kScanChannels* kScanMaxRuns) mingru_scan_kerne
 
 using namespace tlie;
 
-// ``runs``: how many runs a request's rows are cut into (1 to 32); the host picks it from the longest entry of the step.
+// ``runs``: how many runs a request's rows are cut into (1 to 64); the host picks it from the longest entry of the step.  A CTA takes
+// 32 channels, or 16 (and then up to 64 runs) where 32 would leave SMs without a CTA.
 TLIE_EXPORT int tlie_mingru_scan(int dtype, const void* zxg, const float* bias_z, const float* bias_x, float* state, const int* seq_starts,
                                  const int* state_slots, void* out, int entries, int width, int runs, cudaStream_t stream) {
   if (entries <= 0 || width <= 0) return 0;
-  if (runs < 1 || runs > kScanMaxRuns) return (int)cudaErrorInvalidValue;
-  const dim3 grid((width + kScanChannels - 1) / kScanChannels, entries), block(kScanChannels, runs);
+  if (runs < 1 || runs > 64) return (int)cudaErrorInvalidValue;
+  int channels = kScanChannels;
+  if (runs > 1 && (long long)((width + 31) / 32) * entries < device_sm_count()) channels = 16;
+  if (runs * channels > kScanThreads) runs = kScanThreads / channels;
+  const dim3 grid((width + channels - 1) / channels, entries), block(channels, runs);
   if (dtype == TLIE_F32)
     mingru_scan_kernel<float><<<grid, block, 0, stream>>>((const float*)zxg, bias_z, bias_x, state, seq_starts, state_slots, (float*)out, width);
   else

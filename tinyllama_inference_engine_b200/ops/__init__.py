@@ -370,7 +370,7 @@ def attention_step(qkv, positions, token_seq, block_table, inv_freq, rotary_dim:
 
 
 # --- recurrences ---------------------------------------------------------------------------
-GATED_RECURRENCE_MAX_RUNS = 32
+GATED_RECURRENCE_MAX_RUNS = 64
 
 
 def recurrent():
@@ -458,7 +458,7 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     splits, partial = 1, None
     if batch is not None and tokens * 2 <= fast.sm_count():
         reach = min(window, batch.max_seq_len) if window > 0 else batch.max_seq_len
-        splits = max(1, min(2 * fast.sm_count() // tokens, reach // 64, 64))
+        splits = max(1, min(2 * fast.sm_count() // tokens, -(-reach // 32), 64))   # down to one tile of 32 keys per CTA
         if splits > 1:
             partial = fast.mixed_scratch(rows.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32)
     _check(mixed_attention().tlie_mixed_heads_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr,
