@@ -10,7 +10,7 @@
 // PARTS is 1 and the query is the head's own.
 //
 // One CTA per (tile of rows of one request, head), one warp per 16 rows; keys and values stream through shared memory in
-// 64-key tiles (cp.async, two stages where they fit); Q'.K^T and P.V on mma.sync m16n8k16 with 32-bit accumulators, the
+// 64-key tiles (cp.async, a ring of chunks); Q'.K^T and P.V on mma.sync m16n8k16 with 32-bit accumulators, the
 // distance bias, the mask, the running maximum and sum in 32-bit; the output gate in the epilogue.
 //
 // Compile-time: KEY_DIM, VALUE_DIM (multiples of 16), PARTS (key heads per folded query).
@@ -33,13 +33,23 @@ constexpr int kD = KEY_DIM, kVD = VALUE_DIM, kParts = PARTS;
 constexpr int kKeys = 64;
 constexpr int kKRow = kD + 8, kVRow = kVD + 8, kQRow = kParts * kD + 8;   // padded shared-memory rows (elements)
 constexpr size_t kSmemLimit = 227 * 1024;
-constexpr size_t smem_for(int rows, int stages) {
-  return ((size_t)rows * kQRow + (size_t)stages * ((size_t)kParts * kKeys * kKRow + (size_t)kKeys * kVRow)) * sizeof(__nv_bfloat16);
+// Keys pass through shared memory in chunks of a 64-key tile: all PARTS key heads at once with the next tile's chunk in flight (a ring
+// of two) where that fits beside 128 rows of folded queries, else one key head at a time with two chunks in flight (a ring of three).
+// Values pass one tile at a time: two buffers, or as many as the ring where a tile is a single chunk, so that a tile issued ahead
+// never lands in a buffer still being read.  The folded queries of the CTA's rows stay resident.
+constexpr size_t smem_for(int rows, int parts_per_chunk) {
+  const int ring = parts_per_chunk == kParts ? 2 : 3;
+  const int v_buffers = parts_per_chunk == kParts ? ring : 2;
+  return ((size_t)rows * kQRow + (size_t)ring * parts_per_chunk * kKeys * kKRow + (size_t)v_buffers * kKeys * kVRow) * sizeof(__nv_bfloat16);
 }
-constexpr bool fits(int rows, int stages) { return smem_for(rows, stages) <= kSmemLimit; }
-// rows per CTA and stages: the largest that fits shared memory; 0 rows if nothing does (the host then uses the general kernel)
-constexpr int kRows = fits(128, 2) ? 128 : fits(64, 2) ? 64 : fits(32, 2) ? 32 : fits(64, 1) ? 64 : fits(32, 1) ? 32 : fits(16, 1) ? 16 : 0;
-constexpr int kStages = (fits(128, 2) || fits(64, 2) || fits(32, 2)) ? 2 : 1;
+constexpr bool fits(int rows, int parts_per_chunk) { return smem_for(rows, parts_per_chunk) <= kSmemLimit; }
+// rows per CTA: the most that fit shared memory, whole tiles before single key heads; 0 if nothing fits (the host then uses the general kernel)
+constexpr int kRows = (fits(128, kParts) || fits(128, 1)) ? 128 : (fits(64, kParts) || fits(64, 1)) ? 64 : (fits(32, kParts) || fits(32, 1)) ? 32 : fits(16, 1) ? 16 : 0;
+constexpr int kPartsPerChunk = fits(kRows > 0 ? kRows : 16, kParts) ? kParts : 1;
+constexpr int kChunksPerTile = kParts / kPartsPerChunk;
+constexpr int kRing = kPartsPerChunk == kParts ? 2 : 3;
+constexpr int kVBuffers = kChunksPerTile == 1 ? kRing : 2;
+constexpr size_t kChunkElements = (size_t)kPartsPerChunk * kKeys * kKRow;
 constexpr int kWarps = kRows > 0 ? kRows / 16 : 1;
 constexpr int kThreads = kWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -63,42 +73,44 @@ __global__ void fold_queries_kernel(const __nv_bfloat16* __restrict__ rows, int 
   }
 }
 
-__device__ __forceinline__ void load_tile(__nv_bfloat16* k_smem, __nv_bfloat16* v_smem, const __nv_bfloat16* k_pages, long long k_page_stride,
-                                          const __nv_bfloat16* v_pages, long long v_page_stride, const int* table, int key0, int lo, int n_keys,
-                                          int kvh, int page_size, bool mixed) {
-  // a page holds a multiple of 16 keys, so each 16-key quarter of a tile lies in one page
-  long long page_of[kKeys / 16];
-  int slot_of[kKeys / 16];
+// where the four 16-key quarters of a tile lie: a page holds a multiple of 16 keys, so each quarter lies in one page
+struct TileRows {
+  long long page[kKeys / 16];
+  int slot[kKeys / 16];
+};
+
+__device__ __forceinline__ TileRows tile_rows(const int* table, int key0, int lo, int n_keys, int page_size) {
+  TileRows rows;
 #pragma unroll
   for (int h = 0; h < kKeys / 16; ++h) {
     const int k = key0 + 16 * h;
     const bool any = k < n_keys && k + 16 > lo;
-    page_of[h] = any ? table[k / page_size] : 0;
-    slot_of[h] = k % page_size;
+    rows.page[h] = any ? table[k / page_size] : 0;
+    rows.slot[h] = k % page_size;
   }
-  constexpr int kChunks = kD / 8, kVChunks = kVD / 8;
-  for (int idx = threadIdx.x; idx < kParts * kKeys * kChunks; idx += kThreads) {
-    const int chunk = idx % kChunks, row = (idx / kChunks) % kKeys, part = idx / (kChunks * kKeys);
+  return rows;
+}
+
+// one plane's rows of a tile for one head: [64][row] in shared memory, ``width`` elements each
+template <int WIDTH, int ROW>
+__device__ __forceinline__ void load_plane(__nv_bfloat16* smem, const __nv_bfloat16* pages, long long page_stride, const TileRows& rows, int key0, int lo,
+                                           int n_keys, int head, int page_size) {
+  constexpr int kChunks = WIDTH / 8;
+  for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kThreads) {
+    const int chunk = idx % kChunks, row = idx / kChunks;
     const int key = key0 + row, quarter = row >> 4;
     const bool valid = key >= lo && key < n_keys;
-    const int head = mixed ? part : kvh;
-    const long long page = quarter == 0 ? page_of[0] : quarter == 1 ? page_of[1] : quarter == 2 ? page_of[2] : page_of[3];
-    const int slot = (quarter == 0 ? slot_of[0] : quarter == 1 ? slot_of[1] : quarter == 2 ? slot_of[2] : slot_of[3]) + (row & 15);
-    const __nv_bfloat16* src = k_pages + page * k_page_stride + ((size_t)head * page_size + slot) * kD + chunk * 8;
-    cp_async_16(k_smem + ((size_t)part * kKeys + row) * kKRow + chunk * 8, valid ? src : k_pages, valid);
-  }
-  for (int idx = threadIdx.x; idx < kKeys * kVChunks; idx += kThreads) {
-    const int chunk = idx % kVChunks, row = idx / kVChunks;
-    const int key = key0 + row, quarter = row >> 4;
-    const bool valid = key >= lo && key < n_keys;
-    const long long page = quarter == 0 ? page_of[0] : quarter == 1 ? page_of[1] : quarter == 2 ? page_of[2] : page_of[3];
-    const int slot = (quarter == 0 ? slot_of[0] : quarter == 1 ? slot_of[1] : quarter == 2 ? slot_of[2] : slot_of[3]) + (row & 15);
-    const __nv_bfloat16* src = v_pages + page * v_page_stride + ((size_t)kvh * page_size + slot) * kVD + chunk * 8;
-    cp_async_16(v_smem + (size_t)row * kVRow + chunk * 8, valid ? src : v_pages, valid);
+    const long long page = quarter == 0 ? rows.page[0] : quarter == 1 ? rows.page[1] : quarter == 2 ? rows.page[2] : rows.page[3];
+    const int slot = (quarter == 0 ? rows.slot[0] : quarter == 1 ? rows.slot[1] : quarter == 2 ? rows.slot[2] : rows.slot[3]) + (row & 15);
+    const __nv_bfloat16* src = pages + page * page_stride + ((size_t)head * page_size + slot) * WIDTH + chunk * 8;
+    cp_async_16(smem + (size_t)row * ROW + chunk * 8, valid ? src : pages, valid);
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// two CTAs on an SM where shared memory has room for both and the output accumulators leave the registers for it
+constexpr int kMinBlocks = (kRows > 0 && 2 * smem_for(kRows > 0 ? kRows : 16, kPartsPerChunk) <= kSmemLimit && kVD <= 64) ? 2 : 1;
+
+__global__ void __launch_bounds__(kThreads, kMinBlocks)
     mixed_prefill_kernel(const __nv_bfloat16* __restrict__ folded, const __nv_bfloat16* __restrict__ rows, int row_stride, int gate_offset,
                          const __nv_bfloat16* __restrict__ k_pages, long long k_page_stride, const __nv_bfloat16* __restrict__ v_pages,
                          long long v_page_stride, const int* __restrict__ seq_starts, const int* __restrict__ first_positions,
@@ -106,8 +118,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                          int heads, int kv_heads, int page_size, int window, int mixed) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kRows][kQRow]
-  __nv_bfloat16* kv_smem = q_smem + (size_t)kRows * kQRow;                       // [stages]{K [parts][64][kKRow], V [64][kVRow]}
-  constexpr size_t kStage = (size_t)kParts * kKeys * kKRow + (size_t)kKeys * kVRow;
+  __nv_bfloat16* k_ring = q_smem + (size_t)kRows * kQRow;                        // [kRing][kPartsPerChunk][64][kKRow]
+  __nv_bfloat16* v_ring = k_ring + (size_t)kRing * kChunkElements;               // [kVBuffers][64][kVRow]
   const int seq = blockIdx.y, head = blockIdx.z;
   const int seq_start = seq_starts[seq];
   const int q_len = seq_starts[seq + 1] - seq_start;
@@ -132,16 +144,26 @@ __global__ void __launch_bounds__(kThreads, 1)
     const __nv_bfloat16* src = folded + ((size_t)(row0 + (valid ? row : 0)) * heads + head) * (kParts * kD) + chunk * 8;
     cp_async_16(q_smem + (size_t)row * kQRow + chunk * 8, src, valid);
   }
-  cp_async_commit();
 
   const int first_tile = lo_tile / kKeys;
   const int end_tile = (n_keys + kKeys - 1) / kKeys;
-  auto stage_k = [&](int s) { return kv_smem + (size_t)s * kStage; };
-  auto stage_v = [&](int s) { return kv_smem + (size_t)s * kStage + (size_t)kParts * kKeys * kKRow; };
-  if (kStages == 2) {
-    load_tile(stage_k(0), stage_v(0), k_pages, k_page_stride, v_pages, v_page_stride, table, first_tile * kKeys, lo_tile, n_keys, kvh, page_size, mixed != 0);
-    cp_async_commit();
-  }
+  const int chunks = (end_tile - first_tile) * kChunksPerTile;   // chunk c: key heads [c % per tile * kPartsPerChunk, ...) of tile first_tile + c / per tile
+  auto issue = [&](int c) {
+    if (c < chunks) {
+      const int tile = first_tile + c / kChunksPerTile, first_part = (c % kChunksPerTile) * kPartsPerChunk;
+      const TileRows rows_of = tile_rows(table, tile * kKeys, lo_tile, n_keys, page_size);
+#pragma unroll
+      for (int i = 0; i < kPartsPerChunk; ++i)
+        load_plane<kD, kKRow>(k_ring + (size_t)(c % kRing) * kChunkElements + (size_t)i * kKeys * kKRow, k_pages, k_page_stride, rows_of, tile * kKeys, lo_tile, n_keys,
+                              mixed ? first_part + i : kvh, page_size);
+      if (first_part == 0)
+        load_plane<kVD, kVRow>(v_ring + (size_t)((c / kChunksPerTile) % kVBuffers) * kKeys * kVRow, v_pages, v_page_stride, rows_of, tile * kKeys, lo_tile, n_keys, kvh,
+                               page_size);
+    }
+    cp_async_commit();   // a group per chunk, empty past the end, so that the count of groups in flight is the same at every step
+  };
+  issue(0);   // in one group with the folded queries
+  if (kRing == 3) issue(1);
 
   const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
   int my_pos[2], my_lo[2];
@@ -156,48 +178,42 @@ __global__ void __launch_bounds__(kThreads, 1)
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0f, 0.0f};
 
-  for (int tile = first_tile; tile < end_tile; ++tile) {
-    int stage = 0;
-    if (kStages == 2) {
-      stage = (tile - first_tile) & 1;
-      if (tile + 1 < end_tile)
-        load_tile(stage_k(stage ^ 1), stage_v(stage ^ 1), k_pages, k_page_stride, v_pages, v_page_stride, table, (tile + 1) * kKeys, lo_tile, n_keys, kvh,
-                  page_size, mixed != 0);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      load_tile(stage_k(0), stage_v(0), k_pages, k_page_stride, v_pages, v_page_stride, table, tile * kKeys, lo_tile, n_keys, kvh, page_size, mixed != 0);
-      cp_async_commit();
-      cp_async_wait<0>();
-    }
+  float s_frag[kKeys / 8][4];
+  for (int c = 0; c < chunks; ++c) {
+    issue(c + kRing - 1);
+    cp_async_wait<kRing - 1>();   // everything but the chunks issued ahead has landed: chunk c, and its tile's values
     __syncthreads();
-    const __nv_bfloat16* k_smem = stage_k(stage);
-    const __nv_bfloat16* v_smem = stage_v(stage);
+    const int tile = first_tile + c / kChunksPerTile, first_part = (c % kChunksPerTile) * kPartsPerChunk;
+    const __nv_bfloat16* k_smem = k_ring + (size_t)(c % kRing) * kChunkElements;
+    const __nv_bfloat16* v_smem = v_ring + (size_t)((c / kChunksPerTile) % kVBuffers) * kKeys * kVRow;
     const int key0 = tile * kKeys;
     const int warp_last_pos = pos0 + min(warp * 16 + 15, rows_here - 1);
     const int warp_first_pos = pos0 + min(warp * 16, rows_here - 1);
     const int warp_lo = (window > 0 && warp_first_pos - window + 1 > 0) ? warp_first_pos - window + 1 : 0;
     if (key0 <= warp_last_pos && key0 + kKeys > warp_lo) {   // some row of this warp sees some key of this tile
-      float s_frag[kKeys / 8][4];
+      if (first_part == 0) {
 #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j) s_frag[j][0] = s_frag[j][1] = s_frag[j][2] = s_frag[j][3] = 0.0f;
+        for (int j = 0; j < kKeys / 8; ++j) s_frag[j][0] = s_frag[j][1] = s_frag[j][2] = s_frag[j][3] = 0.0f;
+      }
 #pragma unroll 1
-      for (int part = 0; part < kParts; ++part) {
+      for (int i = 0; i < kPartsPerChunk; ++i) {
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
           unsigned qa[4];
-          ldmatrix_x4(qa, q_smem + (size_t)(warp * 16 + (lane & 15)) * kQRow + part * kD + ks * 16 + (lane >> 4) * 8);
+          ldmatrix_x4(qa, q_smem + (size_t)(warp * 16 + (lane & 15)) * kQRow + (first_part + i) * kD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
           for (int jp = 0; jp < kKeys / 16; ++jp) {
             unsigned b[4];
             const int row = (jp * 2 + (lane >> 4)) * 8 + (lane & 7);
             const int col = ks * 16 + ((lane >> 3) & 1) * 8;
-            ldmatrix_x4(b, k_smem + ((size_t)part * kKeys + row) * kKRow + col);
+            ldmatrix_x4(b, k_smem + ((size_t)i * kKeys + row) * kKRow + col);
             mma_bf16(s_frag[jp * 2], qa, b[0], b[1]);
             mma_bf16(s_frag[jp * 2 + 1], qa, b[2], b[3]);
           }
         }
       }
+    }
+    if (first_part + kPartsPerChunk == kParts && key0 <= warp_last_pos && key0 + kKeys > warp_lo) {
       // scores in units of log2: (dot - slope (i - j)) log2 e; keys outside a row's window or after it are masked
       float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-    __syncthreads();   // everyone is done with this stage before it is overwritten
+    __syncthreads();   // everyone is done with this chunk before the ring comes round to its buffer
   }
   cp_async_wait<0>();
 #pragma unroll
@@ -302,7 +318,7 @@ TLIE_EXPORT int tlie_mixed_prefill(const void* rows, int row_stride, int gate_of
   fold_queries_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, mix, scale, (__nv_bfloat16*)folded, heads, heads / kv_heads);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  constexpr size_t smem = smem_for(kRows > 0 ? kRows : 16, kStages);
+  constexpr size_t smem = smem_for(kRows > 0 ? kRows : 16, kPartsPerChunk);
   static bool configured = false;
   if (!configured) {
     e = cudaFuncSetAttribute(mixed_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -691,8 +691,8 @@ def mixed_prefill_takes(batch, rows, page_size: int, parts: int, key_dim: int, v
         return False
     if key_dim % 16 or value_dim % 16 or page_size % 16 or rows.shape[1] % 8 or (gate_offset >= 0 and gate_offset % 2) or batch.num_seqs > 65535:
         return False
-    if ((parts * key_dim + 8) * 16 + parts * 64 * (key_dim + 8) + 64 * (value_dim + 8)) * 2 > 227 * 1024:
-        return False   # not even a tile of 16 rows with one stage fits
+    if ((parts * key_dim + 8) * 16 + 3 * 64 * (key_dim + 8) + (3 if parts == 1 else 2) * 64 * (value_dim + 8)) * 2 > 227 * 1024:
+        return False   # not even 16 rows of folded queries fit beside the rings of keys and values
     return mixed_prefill_library(key_dim, value_dim, parts).tlie_mixed_prefill_tile_rows() > 0
 
 
