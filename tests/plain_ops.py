@@ -141,6 +141,11 @@ def activation(kind, x, out) -> None:
     _store(out, y)
 
 
+def linear_activated(x, weight, out, kind) -> None:
+    linear(x, weight, out)
+    activation(kind, out, out)
+
+
 def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_rows) -> None:
     width = out.shape[1]
     rows = zxg.float()
@@ -205,7 +210,7 @@ def can_accumulate(rows: int, weight) -> bool:
 
 
 _NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample",
-          "can_accumulate", "embedding_positions", "activation", "mingru_scan", "store_kv_planes", "mixed_heads_attention"]
+          "can_accumulate", "embedding_positions", "activation", "linear_activated", "mingru_scan", "store_kv_planes", "mixed_heads_attention"]
 
 
 def install(monkeypatch) -> None:

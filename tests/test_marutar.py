@@ -312,6 +312,32 @@ def test_positioned_embedding_and_activation_kernels(dtype):
         assert torch.allclose(got.cpu().float(), want.float(), atol=1e-5 if dtype == torch.float32 else 0.07, rtol=1e-5 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 5, 16, 40])
+@pytest.mark.parametrize("kind", ["relu_squared", "gelu_tanh", "silu"])
+def test_product_with_activation_behind(rows, kind):
+    """Up to 16 rows the activation is applied in the product's epilogue, beyond by a kernel of its own: the same numbers either way."""
+    from tinyllama_inference_engine_b200 import ops
+
+    g = torch.Generator().manual_seed(rows)
+    x, weight = torch.randn(rows, 72, generator=g).bfloat16(), (torch.randn(200, 72, generator=g) * 0.2).bfloat16()
+    want = torch.zeros(rows, 200, dtype=torch.bfloat16)
+    plain_ops.linear_activated(x, weight, want, kind)
+    got = torch.zeros(rows, 200, dtype=torch.bfloat16, device="cuda")
+    before = ops.launch_count
+    ops.linear_activated(x.cuda(), weight.cuda(), got, kind)
+    assert rows > 16 or ops.launch_count - before == 1
+    assert torch.allclose(got.cpu().float(), want.float(), atol=2e-2, rtol=2e-2)
+    residual, norm_weight = torch.randn(rows, 72, generator=g), 1 + 0.1 * torch.randn(72, generator=g)
+    normed = torch.zeros(rows, 72, dtype=torch.bfloat16)
+    plain_ops.add_rmsnorm(residual.clone(), None, norm_weight, 1e-5, normed)
+    plain_ops.linear_activated(normed, weight, want, kind)
+    lazy = ops.LazyNorm(residual.cuda(), norm_weight.cuda(), 1e-5, None, lambda: None)
+    if rows <= 16:
+        ops.linear_activated(lazy, weight.cuda(), got, kind)
+        assert torch.allclose(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
 # --- the engine on the GPU under every way of cutting the work -------------------------------------------------------------------------------
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

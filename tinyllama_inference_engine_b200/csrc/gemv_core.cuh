@@ -31,7 +31,19 @@ struct GemvArgs {
   // X_PREPARED: x is such a bfloat16 [M, K]; squares [M, square_tiles] are summed into the row's scale with eps
   const float* squares;
   int square_tiles;
+  // STORE_BF16 may apply an activation to the (rounded) product before it is stored: 0 none, 1 the square of relu, 2 gelu in its
+  // tanh form, 3 silu.  The same roundings as a product stored and an elementwise kernel run over it.
+  int activation;
 };
+
+__device__ __forceinline__ float gemv_activate(int kind, float z) {
+  if (kind == 1) {
+    const float r = fmaxf(z, 0.0f);
+    return r * r;
+  }
+  if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
 
 __device__ __forceinline__ uint4 load_stream_16(const void* p) {
   uint4 v;
@@ -143,7 +155,11 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
     }
     const size_t o = (size_t)m * n_rows + n0 + r;
     if (EPI == EPI_STORE_BF16) {
-      if (live) reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum);
+      if (live) {
+        __nv_bfloat16 stored = __float2bfloat16_rn(sum);
+        if (a.activation != 0) stored = __float2bfloat16_rn(gemv_activate(a.activation, __bfloat162float(stored)));
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = stored;
+      }
     } else if (EPI == EPI_STORE_F32) {
       if (live) reinterpret_cast<float*>(a.out)[o] = sum;
     } else if (EPI == EPI_ACCUM) {

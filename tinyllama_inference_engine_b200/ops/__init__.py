@@ -253,6 +253,28 @@ def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
         linear(x.tensor(), weight, out)
 
 
+def linear_activated(x, weight, out, kind: str) -> None:
+    """out = act(x . weight^T), the activation applied to the product as it is stored (rounded to the output's dtype first, as when
+    the product is stored and ``activation`` run over it).  ``x``: a tensor or a ``LazyNorm``.  One kernel for up to 16 bfloat16 rows
+    (norm in front, activation behind); a product and an elementwise kernel otherwise."""
+    lazy = isinstance(x, LazyNorm)
+    if out.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and fast.gemv_fits(out.shape[0], weight.shape[1], norm=lazy, N=None if lazy else weight.shape[0]):
+        if lazy and x.prepared is not None:
+            fast.gemv_fused(x.prepared[0], weight, out, prepared=(x.prepared[1], x.eps), activation=kind)
+            return
+        if lazy:
+            fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), activation=kind)
+            return
+        if x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+            fast.gemv_fused(x, weight, out, activation=kind)
+            return
+    if lazy:
+        norm_linear(x, weight, out)
+    else:
+        linear(x, weight, out)
+    activation(kind, out, out)
+
+
 def can_accumulate(rows: int, weight) -> bool:
     """Whether ``linear_accumulate`` is one kernel for a step of this many rows beyond the fused row limit."""
     return fast.can_accumulate(rows, weight)

@@ -92,7 +92,10 @@ def prepared_norm_buffers(rows: int, width: int, device) -> tuple:
     return (torch.empty((rows, width), dtype=torch.bfloat16, device=device), torch.empty((rows, -(-width // 16)), dtype=torch.float32, device=device))
 
 
-def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None) -> None:
+GEMV_ACTIVATIONS = {None: 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None, activation: str | None = None) -> None:
     """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
 
     norm      None: ``x`` is bfloat16 [M, K].  (norm_weight, eps, rows): ``x`` is the 32-bit residual stream and
@@ -101,6 +104,7 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
               squares, as an earlier "accumulate" with ``prepare`` left them; the operand is the same rmsnorm.
     epilogue  "store": out [M, N] bfloat16 or 32-bit;  "accumulate": out is the 32-bit residual, out += result;
               "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up.
+    activation ("store" into bfloat16 only) "relu_squared", "gelu_tanh" or "silu": applied to the rounded product before it is stored.
     prepare   ("accumulate" only) (norm_weight [N], x_out bfloat16 [M, N], squares_out [M, ceil(N / 16)]): also store
               bfloat16(out * norm_weight) and the rows' sums of squares per 16 columns, for a later call with ``prepared``.
     """
@@ -114,6 +118,8 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
         code = 1 if out.dtype == torch.float32 else 0
     elif epilogue == "accumulate" and out.dtype != torch.float32:
         raise KernelError("gemv_fused accumulates into the 32-bit residual only", code="invalid_dtype")
+    if activation is not None and (epilogue != "store" or out.dtype != torch.bfloat16 or activation not in GEMV_ACTIVATIONS):
+        raise KernelError("gemv_fused applies an activation only when it stores bfloat16", code="invalid_argument")
     if out.shape[1] != (N // 2 if epilogue == "gated" else N):
         raise KernelError("gemv_fused: the output's width does not fit the weight", code="invalid_shape")
     consume = (c_void_p(0), c_int(0))
@@ -141,7 +147,8 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
                 or squares_out.dtype != torch.float32 or squares_out.shape != (M, -(-N // 16)) or not x_out.is_contiguous() or not squares_out.is_contiguous()):
             raise KernelError("gemv_fused: prepare takes a 32-bit norm weight [N], bfloat16 [M, N] and 32-bit [M, ceil(N / 16)], with accumulate", code="invalid_shape")
         emit = (ops._ptr(norm_weight), ops._ptr(x_out), ops._ptr(squares_out))
-    ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, ops._stream()),
+    ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, c_int(GEMV_ACTIVATIONS[activation]),
+                                             ops._stream()),
                "gemv_fused")
 
 

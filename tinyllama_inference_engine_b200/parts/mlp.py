@@ -76,8 +76,8 @@ class DenseMLP(FeedForward):
 
     params: ``hidden_size``, ``intermediate_size``, ``activation`` ("relu_squared", "gelu_tanh" or "silu"; ops.ACTIVATIONS),
     optional ``up_name`` / ``down_name`` (the tensors are ``<prefix>.<name>``: "up" and "down" unless given).
-    The activation is computed in 32-bit on the first product's output, in place.  With few rows the norm in front is applied
-    inside the first product and the residual add inside the second, as the gated feed-forward does.
+    The activation is computed in 32-bit on the first product's (rounded) output.  With few rows the norm in front and the
+    activation behind are applied inside the first product and the residual add inside the second, as the gated feed-forward does.
     """
 
     capturable = True
@@ -112,11 +112,7 @@ class DenseMLP(FeedForward):
     def forward(self, x, ctx, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         act = ws.get("activated", tokens, self.inter, dtype)
-        if isinstance(x, ops.LazyNorm):
-            ops.norm_linear(x, self.w_up, act)
-        else:
-            ops.linear(x, self.w_up, act)
-        ops.activation(self.activation, act, act)
+        ops.linear_activated(x, self.w_up, act, self.activation)   # few rows: norm, product and activation are one kernel
         if accumulate_into is not None:
             ops.linear_accumulate(act, self.w_down, accumulate_into, prepare)
             return None
