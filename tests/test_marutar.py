@@ -463,3 +463,47 @@ def test_generation_in_bfloat16_runs_and_repeats(folders):
     first = generate(folders["wide_heads"], prompts, max_tokens=24, dtype="bfloat16", page_size=16, max_cache_tokens=1024, max_requests=4, max_batch_tokens=64)
     second = generate(folders["wide_heads"], prompts, max_tokens=24, dtype="bfloat16", page_size=16, max_cache_tokens=1024, max_requests=4, max_batch_tokens=64)
     assert first == second and all(len(tokens) == 24 for tokens in first)
+
+
+@pytest.mark.gpu
+def test_command_line_and_trace_program(folders, tmp_path, capsys):
+    """The framework's command line generates, prints logits and builds a model from a config.json with seeded weights; `bin/trace_run`
+    as a child process answers step by step and dumps every layer's output, which matches the plain implementation's trace."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from tinyllama_inference_engine_b200.cli import main
+
+    folder = folders["mixed"]
+    config, tensors = load_plain(folder)
+    prompt = [int(t) for t in np.random.default_rng(12).integers(0, config["vocab"], size=11)]
+    text = ",".join(map(str, prompt))
+    assert main(["generate", str(folder), text, "6", "--dtype", "float32", "--page-size", "16"]) == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert result["generated_tokens"] == _plain_greedy(config, tensors, prompt, 6) and result["prompt_tokens"] == 11
+    assert main(["logits", str(folder), text, "--dtype", "float32"]) == 0
+    logits = torch.tensor(json.loads(capsys.readouterr().out)["logits"])
+    assert torch.allclose(logits, plain_marutar.forward(config, tensors, prompt)[-1], atol=2e-5)
+    assert main(["generate", "-", text, "6", "--dtype", "float32", "--random-config", str(folder / "config.json"), "--weights-seed", str(CONFIGS["mixed"][1])]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["generated_tokens"] == result["generated_tokens"]
+
+    program = Path(__file__).resolve().parent.parent / "bin" / "trace_run"
+    out = tmp_path / "out"
+    tokens = prompt + prompt[::-1]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:13], "want": [12]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[13:], "want": []}, {"id": "b", "tokens": prompt[:2], "want": [1]}], "end": ["a", "b"]}]
+    child = subprocess.run([sys.executable, str(program), "--model", str(folder), "--dtype", "float32", "--out", str(out), "--max-tokens", "128", "--dump-layers"],
+                           input="".join(json.dumps(step) + "\n" for step in steps), capture_output=True, text=True, env=dict(os.environ, PYTHONUNBUFFERED="1"))
+    assert child.returncode == 0 and [line for line in child.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1"]
+    trace = []
+    full = plain_marutar.forward(config, tensors, tokens, trace)
+    got = np.fromfile(out / "0.f32", dtype="<f4")
+    assert float(np.abs(got - full[12].numpy()).max()) <= 3e-5 * float(full.abs().max())
+    layers = np.fromfile(out / "0.layers.f32", dtype="<f4").reshape(len(config["layers"]), 13, config["width"])
+    for index, want in enumerate(trace):
+        assert float(np.abs(layers[index] - want[:13].numpy()).max()) <= 3e-5 * float(want.abs().max()), index
+    other = plain_marutar.forward(config, tensors, prompt[:2])
+    assert float(np.abs(np.fromfile(out / "1.f32", dtype="<f4") - other[1].numpy()).max()) <= 3e-5 * float(other.abs().max())
+
