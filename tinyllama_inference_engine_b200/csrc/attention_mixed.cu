@@ -84,22 +84,45 @@ template <typename T>
 __device__ __forceinline__ void stage_plane(T* __restrict__ dst, int stride, const T* __restrict__ pages, const long long* __restrict__ row_at,
                                             int head_stride, int heads, int count, int width) {
   constexpr int kVec = 16 / sizeof(T);
+  constexpr int kBatch = 8;   // loads a thread has in flight before it stores them: a load followed by its own store would wait for the one before
   if (width % kVec == 0) {
     const int chunks = width / kVec;
-    for (int i = threadIdx.x; i < heads * kMixKeys * chunks; i += kMixThreads) {
-      const int chunk = i % chunks, j = (i / chunks) % kMixKeys, c = i / (chunks * kMixKeys);
-      if (j >= count) continue;
-      const uint4 raw = *reinterpret_cast<const uint4*>(pages + row_at[j] + (size_t)c * head_stride + chunk * kVec);
-      unsigned* out = reinterpret_cast<unsigned*>(dst + (size_t)(c * kMixKeys + j) * stride + chunk * kVec);   // rows are 4-byte aligned, not 16
-      out[0] = raw.x;
-      out[1] = raw.y;
-      out[2] = raw.z;
-      out[3] = raw.w;
+    const int total = heads * kMixKeys * chunks;
+    for (int i0 = threadIdx.x; i0 < total; i0 += kBatch * kMixThreads) {
+      uint4 raw[kBatch];
+      int at[kBatch];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int i = i0 + b * kMixThreads;
+        const int chunk = i % chunks, j = (i / chunks) % kMixKeys, c = i / (chunks * kMixKeys);
+        at[b] = (i < total && j < count) ? (c * kMixKeys + j) * stride + chunk * kVec : -1;
+        if (at[b] >= 0) raw[b] = *reinterpret_cast<const uint4*>(pages + row_at[j] + (size_t)c * head_stride + chunk * kVec);
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        if (at[b] < 0) continue;
+        unsigned* out = reinterpret_cast<unsigned*>(dst + at[b]);   // rows are 4-byte aligned, not 16
+        out[0] = raw[b].x;
+        out[1] = raw[b].y;
+        out[2] = raw[b].z;
+        out[3] = raw[b].w;
+      }
     }
   } else {
-    for (int i = threadIdx.x; i < heads * kMixKeys * width; i += kMixThreads) {
-      const int d = i % width, j = (i / width) % kMixKeys, c = i / (width * kMixKeys);
-      if (j < count) dst[(size_t)(c * kMixKeys + j) * stride + d] = pages[row_at[j] + (size_t)c * head_stride + d];
+    const int total = heads * kMixKeys * width;
+    for (int i0 = threadIdx.x; i0 < total; i0 += kBatch * kMixThreads) {
+      T raw[kBatch];
+      int at[kBatch];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int i = i0 + b * kMixThreads;
+        const int d = i % width, j = (i / width) % kMixKeys, c = i / (width * kMixKeys);
+        at[b] = (i < total && j < count) ? (c * kMixKeys + j) * stride + d : -1;
+        if (at[b] >= 0) raw[b] = pages[row_at[j] + (size_t)c * head_stride + d];
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+        if (at[b] >= 0) dst[at[b]] = raw[b];
     }
   }
 }
@@ -223,8 +246,17 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     for (int h = warp; h < heads; h += warps) {
       float score;
       if (mix) {
-        score = 0.0f;
-        for (int g = 0; g < heads; ++g) score += mix_s[h * heads + g] * raw_s[g * kMixKeys + lane];
+        // four sums side by side: one chain of dependent adds would wait for every load in turn
+        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* weights = mix_s + h * heads;
+        int g = 0;
+#pragma unroll 2
+        for (; g + 4 <= heads; g += 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) part[i] += weights[g + i] * raw_s[(g + i) * kMixKeys + lane];
+        }
+        for (; g < heads; ++g) part[0] += weights[g] * raw_s[g * kMixKeys + lane];
+        score = (part[0] + part[1]) + (part[2] + part[3]);
       } else {
         score = raw_s[h * kMixKeys + lane];
       }
@@ -300,23 +332,44 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
 template <typename T>
 __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* __restrict__ rows, int row_stride, int gate_offset, T* __restrict__ out,
                                    int heads, int value_dim, int splits) {
+  __shared__ float weight_s[64];   // at most 64 parts: each part's e^(max - highest), then divided by the sum of the parts' totals
+  __shared__ float scratch[2];
   const int t = blockIdx.x, h = blockIdx.y;
   const int outputs = heads * value_dim;
   const size_t part_size = (size_t)outputs + 2 * heads;
   const float* mine = partial + (size_t)t * splits * part_size;
-  float highest = -INFINITY;
-  for (int s = 0; s < splits; ++s) highest = fmaxf(highest, mine[s * part_size + outputs + h]);
+  if (threadIdx.x < 32) {   // one warp: a lane per part (two at most), all loads in one round trip
+    const int lane = threadIdx.x;
+    float top[2], sum[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = lane + 32 * i;
+      top[i] = s < splits ? mine[s * part_size + outputs + h] : -INFINITY;
+      sum[i] = s < splits ? mine[s * part_size + outputs + heads + h] : 0.0f;
+    }
+    const float highest = warp_max(fmaxf(top[0], top[1]));
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float weight = expf(top[i] - highest);   // a part that saw no key has maximum -inf: weight 0
+      if (lane + 32 * i < splits) weight_s[lane + 32 * i] = weight;
+      total += sum[i] * weight;
+    }
+    total = warp_sum(total);
+    if (lane == 0) scratch[0] = 1.0f / total;
+  }
+  __syncthreads();
+  const float inv = scratch[0];
   for (int d = threadIdx.x; d < value_dim; d += blockDim.x) {
     const int o = h * value_dim + d;
-    float value = 0.0f, total = 0.0f;
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) {
-      const float* part = mine + s * part_size;
-      const float weight = expf(part[outputs + h] - highest);   // a part that saw no key has maximum -inf: weight 0
-      value += part[o] * weight;
-      total += part[outputs + heads + h] * weight;
+    float value[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) value[i] += mine[(s + i) * part_size + o] * weight_s[s + i];
     }
-    float v = value / total;
+    for (; s < splits; ++s) value[0] += mine[s * part_size + o] * weight_s[s];
+    float v = ((value[0] + value[1]) + (value[2] + value[3])) * inv;
     if (gate_offset >= 0) {
       const float g = to_float(rows[(size_t)t * row_stride + gate_offset + o]);
       v *= 1.0f / (1.0f + expf(-g));
@@ -377,7 +430,7 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
                                            void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window,
                                            float scale, int splits, float* partial, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0 || splits < 1 || splits > 65535 || (splits > 1 && partial == nullptr))
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0 || splits < 1 || splits > 64 || (splits > 1 && partial == nullptr))
     return (int)cudaErrorInvalidValue;
   const int outputs = heads * value_dim;
   if (outputs > 32 * kMixThreads) return (int)cudaErrorInvalidValue;

@@ -481,6 +481,10 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     if batch is not None and tokens * 2 <= fast.sm_count():
         reach = min(window, batch.max_seq_len) if window > 0 else batch.max_seq_len
         splits = max(1, min(2 * fast.sm_count() // tokens, -(-reach // 32), 64))   # down to one tile of 32 keys per CTA
+        if fast.mixed_decode_takes(rows, heads, kv_heads, key_dim, value_dim, gate_offset, mix is not None):
+            fast.mixed_decode(rows, gate_offset, positions, token_seq, table, (k_ptr, k_stride, v_ptr, v_stride), slopes, mix, out, heads, kv_heads, key_dim,
+                              value_dim, cache.page_size, window, scale, splits)
+            return
         if splits > 1:
             partial = fast.mixed_scratch(rows.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32)
     _check(mixed_attention().tlie_mixed_heads_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr,

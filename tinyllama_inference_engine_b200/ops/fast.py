@@ -41,6 +41,8 @@ def build_all() -> list:
     built.append(build_library("tlie_probes", ["probes.cu"]))
     for key_dim, value_dim, parts in DEFAULT_MIXED_PREFILL_SETS:
         built.append(build_library(f"tlie_attn_mixed_k{key_dim}_v{value_dim}_p{parts}", ["attention_mixed_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "PARTS": parts}))
+        built.append(build_library(f"tlie_attn_mixed_decode_k{key_dim}_v{value_dim}_g{parts}", ["attention_mixed_decode.cu"],
+                                   {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "KV_HEADS": parts}))
     return built
 
 
@@ -743,6 +745,47 @@ def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mi
             c_int(heads), c_int(kv_heads), c_int(page_size), c_int(window), ops._stream()),
         "mixed_prefill")
     ops.launch_count += 1   # two kernels: the fold and the attention
+
+
+# --- attention with mixed heads, steps of few rows on the tensor cores ------------------------------------------------------------------
+use_mixed_decode = True
+
+
+def mixed_decode_library(key_dim: int, value_dim: int, kv_heads: int):
+    """The kernel set of one (key width, value width, key/value heads): compiled when a model of these sizes first decodes."""
+    lib = load_library(f"tlie_attn_mixed_decode_k{key_dim}_v{value_dim}_g{kv_heads}", ["attention_mixed_decode.cu"],
+                       {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "KV_HEADS": kv_heads})
+    if not getattr(lib, "_tlie_typed", False):
+        lib.tlie_mixed_decode_smem_bytes.restype = c_longlong
+        lib._tlie_typed = True
+    return lib
+
+
+def mixed_decode_takes(rows, heads: int, kv_heads: int, key_dim: int, value_dim: int, gate_offset: int, mixed: bool) -> bool:
+    """Whether a step of few rows runs its attention with mixed heads on the tensor-core decode kernel: bfloat16, widths that are
+    multiples of 16, at most 16 heads per key/value head, and a tile that fits shared memory."""
+    if not use_mixed_decode or rows.dtype != torch.bfloat16 or key_dim % 16 or value_dim % 16 or heads // kv_heads > 16 or rows.shape[1] % 8:
+        return False
+    if gate_offset >= 0 and gate_offset % 2:
+        return False
+    fixed = 512 + kv_heads * (16 * (key_dim + 8) + 32 * (key_dim + 8) + 32 * (value_dim + 8) + 16 * 40) * 2
+    return fixed + heads * 32 * 4 + (heads * heads * 4 if mixed else 0) + 3 * heads * 4 + 16 <= 200 * 1024
+
+
+def mixed_decode(rows, gate_offset: int, positions, token_seq, block_table, planes, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                 page_size: int, window: int, scale: float, splits: int) -> None:
+    """Attention with mixed heads for a step of few rows (csrc/attention_mixed_decode.cu).  ``planes`` as in ``mixed_prefill``;
+    ``splits``: CTAs that share a row's key tiles (their parts are merged by a second kernel)."""
+    ops = _ops()
+    tokens = rows.shape[0]
+    partial = mixed_scratch(rows.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32) if splits > 1 else None
+    k_ptr, k_stride, v_ptr, v_stride = planes
+    ops._check(
+        mixed_decode_library(key_dim, value_dim, kv_heads).tlie_mixed_decode(
+            ops._ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr, c_longlong(v_stride), ops._i32(positions, "positions"),
+            ops._i32(token_seq, "token_seq"), ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(slopes), ops._ptr(mix), ops._ptr(out),
+            c_int(tokens), c_int(heads), c_int(page_size), c_int(window), c_float(scale), c_int(splits), ops._ptr(partial), ops._stream()),
+        "mixed_decode")
 
 
 if os.environ.get("TLIE_SKINNY", "0") == "1":
