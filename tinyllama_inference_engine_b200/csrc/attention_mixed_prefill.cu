@@ -55,19 +55,40 @@ constexpr int kThreads = kWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // folded[t, h, p, :] = scale * sum over the query heads g of key/value head c(p) of M[h, g] q[t, g, :]   (no mix: scale * q[t, h, :])
-__global__ void fold_queries_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, const float* __restrict__ mix, float scale,
-                                    __nv_bfloat16* __restrict__ folded, int heads, int group) {
+// A CTA per token: its queries and the mixing matrix wait in shared memory, a thread takes outputs of one (head, part) at
+// neighbouring elements, so a warp reads one mixing weight (broadcast) and 32 neighbouring query elements per step.
+__global__ void __launch_bounds__(256) fold_queries_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, const float* __restrict__ mix, float scale,
+                                                           __nv_bfloat16* __restrict__ folded, int heads, int group) {
+  extern __shared__ float fold_smem[];
+  float* q_s = fold_smem;                 // [heads][kD]
+  float* mix_s = q_s + heads * kD;        // [heads][heads]
   const int t = blockIdx.x;
   const __nv_bfloat16* q = rows + (size_t)t * row_stride;
   __nv_bfloat16* dst = folded + (size_t)t * heads * kParts * kD;
+  for (int i = threadIdx.x; i < heads * kD / 2; i += blockDim.x) {
+    const float2 pair = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(q)[i]);
+    q_s[2 * i] = pair.x;
+    q_s[2 * i + 1] = pair.y;
+  }
+  if (mix != nullptr)
+    for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) mix_s[i] = mix[i];
+  __syncthreads();
   for (int i = threadIdx.x; i < heads * kParts * kD; i += blockDim.x) {
     const int d = i % kD, p = (i / kD) % kParts, h = i / (kD * kParts);
     float sum;
     if (mix == nullptr) {
-      sum = __bfloat162float(q[h * kD + d]);
+      sum = q_s[h * kD + d];
     } else {
-      sum = 0.0f;
-      for (int g = p * group; g < (p + 1) * group; ++g) sum += mix[h * heads + g] * __bfloat162float(q[g * kD + d]);
+      float part[2] = {0.0f, 0.0f};
+      const float* weights = mix_s + h * heads + p * group;
+      const float* column = q_s + (size_t)p * group * kD + d;
+      int g = 0;
+      for (; g + 2 <= group; g += 2) {
+        part[0] += weights[g] * column[g * kD];
+        part[1] += weights[g + 1] * column[(g + 1) * kD];
+      }
+      if (g < group) part[0] += weights[g] * column[g * kD];
+      sum = part[0] + part[1];
     }
     dst[i] = __float2bfloat16_rn(sum * scale);
   }
@@ -315,8 +336,15 @@ TLIE_EXPORT int tlie_mixed_prefill(const void* rows, int row_stride, int gate_of
   if (kRows == 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size % 16 != 0 || heads > 65535 || entries > 65535 ||
       (mix != nullptr ? kParts != kv_heads : kParts != 1) || row_stride % 8 != 0 || (gate_offset >= 0 && gate_offset % 2 != 0))
     return (int)cudaErrorInvalidValue;
-  fold_queries_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, mix, scale, (__nv_bfloat16*)folded, heads, heads / kv_heads);
-  cudaError_t e = cudaGetLastError();
+  const size_t fold_smem = ((size_t)heads * kD + (mix != nullptr ? (size_t)heads * heads : 0)) * sizeof(float);
+  if (fold_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
+  if (fold_smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(fold_queries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fold_smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  fold_queries_kernel<<<tokens, 256, fold_smem, stream>>>((const __nv_bfloat16*)rows, row_stride, mix, scale, (__nv_bfloat16*)folded, heads, heads / kv_heads);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   constexpr size_t smem = smem_for(kRows > 0 ? kRows : 16, kPartsPerChunk);
   static bool configured = false;
