@@ -9,7 +9,7 @@ cache stream of the model's order list.  Streams with the same need form a *grou
   keys and values are two equal planes).  Equal planes share one device tensor
   ``[stream, page, plane, head, slot, width]``; unequal ones get a tensor each,
   ``[stream, page, head, slot, width]``.  Groups with different needs have pools of their own.  Pages go back to the pool when the request ends, and, in a
-  window group, as soon as every later query is past them; they are handed out again
+  window group, as soon as every later query is past them (the pages of the first ``keep_first`` tokens stay); they are handed out again
   without being cleared (positions beyond a request's length are never read).
 * a **state group** holds one tensor of fixed size per request *slot* and stream,
   ``[stream, slot, *state_shape]`` in 32-bit, zeroed when a request is admitted.
@@ -58,10 +58,16 @@ class PageGroup:
         return max(0, -(-new_total // self.page_size) - len(table))
 
     def first_needed_page(self, computed: int) -> int:
-        """Lowest logical page any query at position >= computed can still read."""
+        """Lowest logical page of the window that any query at position >= computed can still read."""
         if self.need.window <= 0:
             return 0
         return max(0, computed - self.need.window + 1) // self.page_size
+
+    def kept_pages(self) -> int:
+        """Logical pages at the start of a request that stay whatever the window has passed (they hold its first ``keep_first`` tokens)."""
+        if self.need.window <= 0 or self.need.keep_first <= 0:
+            return 0
+        return -(-self.need.keep_first // self.page_size)
 
 
 class StateGroup:
@@ -199,7 +205,7 @@ class CacheManager:
             return
         for group in self.page_groups:
             table = record.tables.get(group.index, [])
-            passed = [i for i in range(min(group.first_needed_page(new_total), len(table))) if table[i] >= 0]
+            passed = [i for i in range(group.kept_pages(), min(group.first_needed_page(new_total), len(table))) if table[i] >= 0]
             if passed:
                 pages = [table[i] for i in passed]
                 self._give_back(group, pages, request_id)

@@ -64,4 +64,26 @@ def load_model_config(model_dir: str | Path) -> tuple[Architecture, Any]:
     """Read ``model_dir/config.json`` and return (architecture, typed configuration)."""
     data = read_config_json(model_dir)
     architecture = architecture_for(data)
-    return architecture, architecture.config_class.from_dict(data)
+    config = architecture.config_class.from_dict(data)
+    if hasattr(config, "with_tensor_shapes"):
+        # a design may leave sizes to its tensors' shapes: the configuration is completed from the weight files' headers
+        config = config.with_tensor_shapes(tensor_shapes(model_dir))
+    return architecture, config
+
+
+def tensor_shapes(model_dir: str | Path) -> dict:
+    """name -> shape of every tensor in the folder's weight files (headers only; empty if the folder has none)."""
+    from ..weights.safetensors_io import SafetensorsFile
+
+    folder = Path(model_dir)
+    if not folder.is_dir():
+        return {}
+    shapes: dict = {}
+    for path in sorted(folder.glob("*.safetensors")):
+        file = SafetensorsFile(path)
+        try:
+            for name in file.names():
+                shapes[name] = tuple(file.shape(name))
+        finally:
+            file.close()
+    return shapes

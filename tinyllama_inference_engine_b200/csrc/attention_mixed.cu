@@ -4,9 +4,12 @@
 // For query token t at position i of its request, key position j, query head g (key/value head g / (H / G)):
 //   raw_g(i, j)   = (q_g . k_j) * scale - slope_g * (i - j)              (slopes optional)
 //   mixed_h(i, j) = sum_g M[h, g] raw_g(i, j)                             (M optional: H x H, row h mixes into head h)
-//   visible: 0 <= i - j, and i - j < window if window > 0
+//   visible: 0 <= i - j, and i - j < window if window > 0; with keep_first > 0 the keys j < keep_first stay visible behind the window
 //   out_h = softmax_j(mixed_h) . v_j                                      (values of value_dim, keys of key_dim)
-//   out   = concat_h(out_h) * sigmoid(gate)                               (gate optional: H * value_dim columns of the same row)
+//   out   = concat_h(out_h) * sigmoid(gate)                               (gate optional: H * value_dim columns of the same row, or H: one per head)
+// ``sinks`` (optional, one per head): the softmax's denominator also holds exp(sink_h), a weight that belongs to no key.
+// ``v_row_stride``: elements between two slots of the value plane (value_dim unless the values are a part of wider rows, as when
+// they are the leading columns of the keys themselves).
 // The mix needs every head's score of a (query, key) pair in one place, so a CTA owns one query token with all its heads: per
 // tile of 32 keys the warps take the heads' raw scores (a lane per key), then the mixed rows with their running maximum and sum
 // (a warp per head), then every thread adds the tile into its share of the H * value_dim outputs.  Tiles start at the first
@@ -41,6 +44,93 @@ __global__ void store_kv_planes_kernel(const T* __restrict__ rows, int row_strid
   for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
     const int head = i / value_dim, d = i - head * value_dim;
     v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = row[v_offset + i];
+  }
+}
+
+// Queries and keys divided by their root mean square per head (optionally times a weight), then the cache write: the normalised
+// keys into the key plane and ``kv_heads * value_dim`` columns from ``v_offset`` into the value plane as they are (with
+// ``v_offset == k_offset`` the values are the keys before the norm).  q is normalised in place.  A warp per head.
+template <typename T>
+__global__ void __launch_bounds__(128) normed_store_kernel(T* __restrict__ rows, int row_stride, int k_offset, int v_offset, const float* __restrict__ q_weight,
+                                                           const float* __restrict__ k_weight, float eps, const int* __restrict__ positions,
+                                                           const int* __restrict__ token_seq, const int* __restrict__ block_table, int table_stride,
+                                                           T* __restrict__ k_pages, long long k_page_stride, T* __restrict__ v_pages, long long v_page_stride,
+                                                           int heads, int kv_heads, int key_dim, int value_dim, int page_size, int write_cache) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int page = write_cache ? block_table[(size_t)token_seq[t] * table_stride + pos / page_size] : -1;
+  const int slot = pos % page_size;
+  T* row = rows + (size_t)t * row_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (page >= 0)   // values first: they may be the keys, which are still as the product left them
+    for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+      const int head = i / value_dim, d = i - head * value_dim;
+      v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = row[v_offset + i];
+    }
+  for (int h = warp; h < heads + kv_heads; h += warps) {
+    const bool is_key = h >= heads;
+    T* head_row = is_key ? row + k_offset + (h - heads) * key_dim : row + h * key_dim;
+    const float* weight = is_key ? k_weight : q_weight;
+    float squares = 0.0f;
+    for (int d = lane; d < key_dim; d += 32) {
+      const float v = to_float(head_row[d]);
+      squares += v * v;
+    }
+    const float inv = rsqrtf(warp_sum(squares) / (float)key_dim + eps);
+    for (int d = lane; d < key_dim; d += 32) {
+      const T v = from_float<T>(to_float(head_row[d]) * inv * (weight ? weight[d] : 1.0f));
+      if (!is_key)
+        head_row[d] = v;
+      else if (page >= 0)
+        k_pages[(size_t)page * k_page_stride + ((size_t)(h - heads) * page_size + slot) * key_dim + d] = v;
+    }
+  }
+}
+
+// Latent attention's cache write and rotation.  A row holds ``heads`` queries of [plain | rot] and, from ``latent_offset``, the
+// down projection [rank | rot].  The first ``rank`` columns are normalised (RMS, weight) into the latent; the last ``rot`` are a key
+// part that all heads share and that is rotated: pairs (2i, 2i + 1) of its first ``rot_dims`` columns turn by position * inv_freq[i]
+// (32-bit angles).  [latent | rotated part] goes into the token's cache row; the queries' rotated parts go into ``queries``
+// [T, heads, rank + rot] behind the ``rank`` columns that the product with the keys' expansion fills.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_store_kernel(const T* __restrict__ rows, int row_stride, int latent_offset, const float* __restrict__ weight, float eps,
+                                                           const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
+                                                           const int* __restrict__ token_seq, const int* __restrict__ block_table, int table_stride,
+                                                           T* __restrict__ pages, long long page_stride, int heads, int plain, int rot, int rank, int page_size,
+                                                           int write_cache, T* __restrict__ queries) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int page = write_cache ? block_table[(size_t)token_seq[t] * table_stride + pos / page_size] : -1;
+  const T* row = rows + (size_t)t * row_stride;
+  T* cached = page >= 0 ? pages + (size_t)page * page_stride + (size_t)(pos % page_size) * (rank + rot) : nullptr;
+  float squares = 0.0f;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    const float v = to_float(row[latent_offset + d]);
+    squares += v * v;
+  }
+  const float inv = rsqrtf(block_sum(squares, scratch) / (float)rank + eps);
+  if (cached)
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) cached[d] = from_float<T>(to_float(row[latent_offset + d]) * inv * weight[d]);
+  // the rot parts: the shared key part is vector ``heads`` and goes into the cache row, the queries' parts are vectors 0 .. heads - 1
+  // and go behind the ``rank`` columns of their head in ``queries``; a thread per pair of columns
+  const int pairs = rot / 2;
+  T* query_row = queries + (size_t)t * heads * (rank + rot);
+  for (int i = threadIdx.x; i < (heads + 1) * pairs; i += blockDim.x) {
+    const int vector = i / pairs, pair = i - vector * pairs;
+    const T* at = vector < heads ? row + vector * (plain + rot) + plain : row + latent_offset + rank;
+    T* to = vector < heads ? query_row + vector * (rank + rot) + rank : (cached ? cached + rank : nullptr);
+    if (!to) continue;
+    if (2 * pair + 1 < rot_dims) {
+      float sine, cosine;
+      sincosf((float)pos * inv_freq[pair], &sine, &cosine);
+      const float a = to_float(at[2 * pair]), b = to_float(at[2 * pair + 1]);
+      to[2 * pair] = from_float<T>(a * cosine - b * sine);
+      to[2 * pair + 1] = from_float<T>(b * cosine + a * sine);
+    } else {   // columns that do not rotate
+      to[2 * pair] = at[2 * pair];
+      to[2 * pair + 1] = at[2 * pair + 1];
+    }
   }
 }
 
@@ -82,10 +172,10 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const __nv
 // 16 bytes per load where the width allows it: all of a thread's loads are in flight together.
 template <typename T>
 __device__ __forceinline__ void stage_plane(T* __restrict__ dst, int stride, const T* __restrict__ pages, const long long* __restrict__ row_at,
-                                            int head_stride, int heads, int count, int width) {
+                                            int head_stride, int heads, int count, int width, bool aligned) {
   constexpr int kVec = 16 / sizeof(T);
   constexpr int kBatch = 8;   // loads a thread has in flight before it stores them: a load followed by its own store would wait for the one before
-  if (width % kVec == 0) {
+  if (width % kVec == 0 && aligned) {
     const int chunks = width / kVec;
     const int total = heads * kMixKeys * chunks;
     for (int i0 = threadIdx.x; i0 < total; i0 += kBatch * kMixThreads) {
@@ -160,7 +250,8 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     const T* __restrict__ rows, int row_stride, int gate_offset, const T* __restrict__ k_pages, long long k_page_stride,
     const T* __restrict__ v_pages, long long v_page_stride, const int* __restrict__ positions, const int* __restrict__ token_seq,
     const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, const float* __restrict__ mix, T* __restrict__ out,
-    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale, float* __restrict__ partial, int staged) {
+    int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window, float scale, float* __restrict__ partial, int staged,
+    int keep_first, int gate_per_head, const float* __restrict__ sinks, int v_row_stride) {
   extern __shared__ __align__(16) unsigned char smem_bytes[];
   long long* k_at = reinterpret_cast<long long*>(smem_bytes);   // [32] where a key's row starts in its plane (head 0)
   long long* v_at = k_at + kMixKeys;
@@ -201,32 +292,36 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     const int o = tid + i * kMixThreads;
     acc[i] = 0.0f;
     head_of[i] = o < outputs ? o / value_dim : 0;
-    value_at[i] = (head_of[i] / group) * page_size * value_dim + (o - head_of[i] * value_dim);
+    value_at[i] = (head_of[i] / group) * page_size * v_row_stride + (o - head_of[i] * value_dim);
     staged_at[i] = (head_of[i] / group) * kMixKeys * value_dim + (o - head_of[i] * value_dim);
   }
 
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   // With gridDim.y > 1 the row's key tiles are dealt to that many CTAs in runs; each leaves its unnormalised sums, maxima and
   // totals in ``partial`` and merge_mixed_kernel puts them together.
+  // The visible keys are numbered 0, 1, ...: first the ``kept`` keys that stay visible behind the window, then the window's.
+  const int kept = min(keep_first, lo);
+  const int visible = kept + (pos - lo + 1);
   const int splits = gridDim.y;
-  const int tiles = (pos - lo) / kMixKeys + 1;
+  const int tiles = (visible + kMixKeys - 1) / kMixKeys;
   const int tiles_each = (tiles + splits - 1) / splits;
-  const int first_key = lo + blockIdx.y * tiles_each * kMixKeys;
-  const int last_key = min(pos, first_key + tiles_each * kMixKeys - 1);
+  const int first_key = blockIdx.y * tiles_each * kMixKeys;
+  const int last_key = min(visible - 1, first_key + tiles_each * kMixKeys - 1);
+  const bool v_aligned = (v_row_stride * (int)sizeof(T)) % 16 == 0 && (v_page_stride * (long long)sizeof(T)) % 16 == 0;
   for (int base = first_key; base <= last_key; base += kMixKeys) {
     const int count = min(kMixKeys, last_key - base + 1);
     __syncthreads();   // the tile before is done with k_at / v_at (and, the first time, q_s and the running sums are in place)
     if (tid < count) {
-      const int key = base + tid;
+      const int key = base + tid < kept ? base + tid : lo + (base + tid - kept);
       const long long page = table[key / page_size];
       const int slot = key % page_size;
       k_at[tid] = page * k_page_stride + (long long)slot * key_dim;
-      v_at[tid] = page * v_page_stride + (long long)slot * value_dim;
+      v_at[tid] = page * v_page_stride + (long long)slot * v_row_stride;
     }
     __syncthreads();
     if (staged) {
-      stage_plane(k_t, k_stride, k_pages, k_at, page_size * key_dim, kv_heads, count, key_dim);
-      stage_plane(v_t, value_dim, v_pages, v_at, page_size * value_dim, kv_heads, count, value_dim);
+      stage_plane(k_t, k_stride, k_pages, k_at, page_size * key_dim, kv_heads, count, key_dim, true);
+      stage_plane(v_t, value_dim, v_pages, v_at, page_size * v_row_stride, kv_heads, count, value_dim, v_aligned);
       __syncthreads();
     }
     // raw scores: a warp per head, a lane per key
@@ -237,7 +332,7 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
           raw = dot_staged(q_s + g * key_dim, k_t + (size_t)((g / group) * kMixKeys + lane) * k_stride, key_dim) * scale;
         else
           raw = dot_row(q_s + g * key_dim, k_pages + k_at[lane] + (size_t)(g / group) * page_size * key_dim, key_dim) * scale;
-        if (slopes) raw -= slopes[g] * (float)(pos - (base + lane));
+        if (slopes) raw -= slopes[g] * (float)(pos - (base + lane < kept ? base + lane : lo + (base + lane - kept)));
       }
       raw_s[g * kMixKeys + lane] = raw;
     }
@@ -313,13 +408,23 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
     }
     return;
   }
+  for (int h = tid; h < heads; h += kMixThreads) {   // what an accumulator of head h is multiplied by: 1 / the softmax's denominator
+    if (sinks) {
+      const float top = fmaxf(max_s[h], sinks[h]);
+      const float shrink = expf(max_s[h] - top);
+      rescale_s[h] = shrink / (sum_s[h] * shrink + expf(sinks[h] - top));
+    } else {
+      rescale_s[h] = 1.0f / sum_s[h];
+    }
+  }
+  __syncthreads();
 #pragma unroll
   for (int i = 0; i < ACC; ++i) {
     const int o = tid + i * kMixThreads;
     if (o < outputs) {
-      float v = acc[i] / sum_s[head_of[i]];
+      float v = acc[i] * rescale_s[head_of[i]];
       if (gate_offset >= 0) {
-        const float g = to_float(row[gate_offset + o]);
+        const float g = to_float(row[gate_offset + (gate_per_head ? head_of[i] : o)]);
         v *= 1.0f / (1.0f + expf(-g));
       }
       out[(size_t)t * outputs + o] = from_float<T>(v);
@@ -331,7 +436,7 @@ __global__ void __launch_bounds__(kMixThreads) mixed_heads_attention_kernel(
 // (row, head), a thread per output element: its loads over the parts do not depend on one another.
 template <typename T>
 __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* __restrict__ rows, int row_stride, int gate_offset, T* __restrict__ out,
-                                   int heads, int value_dim, int splits) {
+                                   int heads, int value_dim, int splits, int gate_per_head, const float* __restrict__ sinks) {
   __shared__ float weight_s[64];   // at most 64 parts: each part's e^(max - highest), then divided by the sum of the parts' totals
   __shared__ float scratch[2];
   const int t = blockIdx.x, h = blockIdx.y;
@@ -347,7 +452,7 @@ __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* _
       top[i] = s < splits ? mine[s * part_size + outputs + h] : -INFINITY;
       sum[i] = s < splits ? mine[s * part_size + outputs + heads + h] : 0.0f;
     }
-    const float highest = warp_max(fmaxf(top[0], top[1]));
+    const float highest = sinks ? fmaxf(warp_max(fmaxf(top[0], top[1])), sinks[h]) : warp_max(fmaxf(top[0], top[1]));
     float total = 0.0f;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -356,6 +461,7 @@ __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* _
       total += sum[i] * weight;
     }
     total = warp_sum(total);
+    if (sinks) total += expf(sinks[h] - highest);
     if (lane == 0) scratch[0] = 1.0f / total;
   }
   __syncthreads();
@@ -371,7 +477,7 @@ __global__ void merge_mixed_kernel(const float* __restrict__ partial, const T* _
     for (; s < splits; ++s) value[0] += mine[s * part_size + o] * weight_s[s];
     float v = ((value[0] + value[1]) + (value[2] + value[3])) * inv;
     if (gate_offset >= 0) {
-      const float g = to_float(rows[(size_t)t * row_stride + gate_offset + o]);
+      const float g = to_float(rows[(size_t)t * row_stride + gate_offset + (gate_per_head ? h : o)]);
       v *= 1.0f / (1.0f + expf(-g));
     }
     out[(size_t)t * outputs + o] = from_float<T>(v);
@@ -382,7 +488,8 @@ template <typename T, int ACC>
 static int launch_mixed(const void* rows, int row_stride, int gate_offset, const void* k_pages, long long k_page_stride, const void* v_pages,
                         long long v_page_stride, const int* positions, const int* token_seq, const int* block_table, int table_stride,
                         const float* slopes, const float* mix, void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
-                        int page_size, int window, float scale, size_t smem, int splits, float* partial, cudaStream_t stream) {
+                        int page_size, int window, float scale, size_t smem, int splits, float* partial, int keep_first, int gate_per_head,
+                        const float* sinks, int v_row_stride, cudaStream_t stream) {
   auto kernel = mixed_heads_attention_kernel<T, ACC>;
   // room for a tile's keys and values of every key/value head behind the 32-bit part; without it rows are read from global memory
   const size_t tiles = (size_t)kv_heads * kMixKeys * ((size_t)staged_key_stride<T>(key_dim) + value_dim) * sizeof(T);
@@ -395,10 +502,11 @@ static int launch_mixed(const void* rows, int row_stride, int gate_offset, const
   }
   kernel<<<dim3(tokens, splits), kMixThreads, smem, stream>>>((const T*)rows, row_stride, gate_offset, (const T*)k_pages, k_page_stride, (const T*)v_pages,
                                                               v_page_stride, positions, token_seq, block_table, table_stride, slopes, mix, (T*)out, heads,
-                                                              kv_heads, key_dim, value_dim, page_size, window, scale, partial, staged);
+                                                              kv_heads, key_dim, value_dim, page_size, window, scale, partial, staged, keep_first, gate_per_head,
+                                                              sinks, v_row_stride);
   if (splits > 1)
     merge_mixed_kernel<T><<<dim3(tokens, heads), value_dim >= 128 ? 128 : (value_dim > 32 ? 64 : 32), 0, stream>>>(partial, (const T*)rows, row_stride, gate_offset,
-                                                                                                                  (T*)out, heads, value_dim, splits);
+                                                                                                                  (T*)out, heads, value_dim, splits, gate_per_head, sinks);
   return (int)cudaGetLastError();
 }
 
@@ -428,8 +536,10 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
                                            long long k_page_stride, const void* v_pages, long long v_page_stride, const int* positions,
                                            const int* token_seq, const int* block_table, int table_stride, const float* slopes, const float* mix,
                                            void* out, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int page_size, int window,
-                                           float scale, int splits, float* partial, cudaStream_t stream) {
+                                           float scale, int splits, float* partial, int keep_first, int gate_per_head, const float* sinks,
+                                           int v_row_stride, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (keep_first < 0 || v_row_stride < value_dim) return (int)cudaErrorInvalidValue;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || key_dim <= 0 || value_dim <= 0 || splits < 1 || splits > 64 || (splits > 1 && partial == nullptr))
     return (int)cudaErrorInvalidValue;
   const int outputs = heads * value_dim;
@@ -439,7 +549,8 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
 #define TLIE_MIXED(T, ACC)                                                                                                                    \
   return launch_mixed<T, ACC>(rows, row_stride, gate_offset, k_pages, k_page_stride, v_pages, v_page_stride, positions, token_seq, block_table, \
-                              table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, splits, partial, stream)
+                              table_stride, slopes, mix, out, tokens, heads, kv_heads, key_dim, value_dim, page_size, window, scale, smem, splits, partial, \
+                              keep_first, gate_per_head, sinks, v_row_stride, stream)
   if (dtype == TLIE_F32) {
     if (outputs <= 4 * kMixThreads) TLIE_MIXED(float, 4);
     if (outputs <= 8 * kMixThreads) TLIE_MIXED(float, 8);
@@ -451,4 +562,36 @@ TLIE_EXPORT int tlie_mixed_heads_attention(int dtype, const void* rows, int row_
   if (outputs <= 16 * kMixThreads) TLIE_MIXED(__nv_bfloat16, 16);
   TLIE_MIXED(__nv_bfloat16, 32);
 #undef TLIE_MIXED
+}
+
+// q (in place) and k divided by their root mean square per head, k into the key plane, the value columns into the value plane.
+TLIE_EXPORT int tlie_normed_store(int dtype, void* rows, int row_stride, int k_offset, int v_offset, const float* q_weight, const float* k_weight, float eps,
+                                  const int* positions, const int* token_seq, const int* block_table, int table_stride, void* k_pages, long long k_page_stride,
+                                  void* v_pages, long long v_page_stride, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int page_size,
+                                  int write_cache, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == TLIE_F32)
+    normed_store_kernel<float><<<tokens, 128, 0, stream>>>((float*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, positions, token_seq, block_table,
+                                                           table_stride, (float*)k_pages, k_page_stride, (float*)v_pages, v_page_stride, heads, kv_heads, key_dim,
+                                                           value_dim, page_size, write_cache);
+  else
+    normed_store_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, positions, token_seq,
+                                                                   block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride, (__nv_bfloat16*)v_pages,
+                                                                   v_page_stride, heads, kv_heads, key_dim, value_dim, page_size, write_cache);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_latent_store(int dtype, const void* rows, int row_stride, int latent_offset, const float* weight, float eps, const float* inv_freq, int rot_dims,
+                                  const int* positions, const int* token_seq, const int* block_table, int table_stride, void* pages, long long page_stride,
+                                  int tokens, int heads, int plain, int rot, int rank, int page_size, int write_cache, void* queries, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || (rot & 1)) return (int)cudaErrorInvalidValue;
+  if (dtype == TLIE_F32)
+    latent_store_kernel<float><<<tokens, 128, 0, stream>>>((const float*)rows, row_stride, latent_offset, weight, eps, inv_freq, rot_dims, positions, token_seq, block_table,
+                                                           table_stride, (float*)pages, page_stride, heads, plain, rot, rank, page_size, write_cache, (float*)queries);
+  else
+    latent_store_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, latent_offset, weight, eps, inv_freq, rot_dims, positions, token_seq,
+                                                                   block_table, table_stride, (__nv_bfloat16*)pages, page_stride, heads, plain, rot, rank, page_size,
+                                                                   write_cache, (__nv_bfloat16*)queries);
+  return (int)cudaGetLastError();
 }

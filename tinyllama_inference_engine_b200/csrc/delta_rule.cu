@@ -1,0 +1,264 @@
+// The gated delta rule with one decay per head and key channel, over the rows of a step, with the state a request carries.
+//
+// Per head, with a state S [dim x vdim] (32-bit, zero for a new request) and per token q, k (unit vectors, q scaled), v,
+// beta in (0, 1) and a decay g in (0, 1) per key channel:
+//     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (the read-out sees the token's own write)
+// Every column of S is independent of the others (S[:, j] sees v_j and u_j only), so a column is owned by a group of 8
+// lanes that split the key channels; a token costs a group three partial dot products (k . S_j, q . S_j, q . k, reduced
+// together by shuffles) and one pass of updates.  o is worked out as q . (g S)_j + (q . k) u_j.
+//
+// Kernels:
+//   delta_prepare    per token: the short causal convolution of q, k, v over time (the taps before an entry's first row come
+//                    from the request's convolution state) with silu, unit norms of q and k per head, q's scale,
+//                    beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)): all 32-bit, into one row of ``prep``
+//   delta_conv_state per entry: the last taps - 1 inputs of the convolution, kept for the next step
+//   delta_rule       the recurrence: one CTA per (entry, head, 16 columns), rows in order, the next row's operands fetched
+//                    while the current one is worked on
+//   delta_gate_norm  per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
+//
+// State of a request (32-bit words): for every head the matrix in the order the recurrence reads it,
+// [(dim + 7) / 8][vdim][8] (key channel 8 i + l at [i][j][l]), then the convolution's inputs [taps - 1][channels].
+#include "common.cuh"
+
+namespace tlie {
+
+constexpr int kDeltaLanes = 8;       // lanes that share a column of the state
+constexpr int kDeltaColumns = 16;    // columns per CTA
+constexpr int kDeltaThreads = kDeltaLanes * kDeltaColumns;
+constexpr int kDeltaMaxTaps = 8;
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// prep row: [q: G dim | k: G dim | v: H vdim | beta: H | decay: H dim]
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict__ rows, int row_stride, int beta_offset, const T* __restrict__ a, const float* __restrict__ taps_w,
+                                                            const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
+                                                            long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
+                                                            const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep,
+                                                            int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale) {
+  extern __shared__ float conv_s[];   // [channels] the convolved and activated q, k, v of this token
+  __shared__ float inv_s[64];         // 1 / norm of every q and k head
+  const int t = blockIdx.x;
+  const int entry = token_seq[t];
+  const int first = seq_starts[entry];
+  const int r = t - first;
+  const int qk = kv_heads * dim;
+  const int channels = 2 * qk + heads * vdim;
+  const float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float sum = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = r - (taps - 1) + j;   // row of the entry this tap reads; negative: before this step
+      const float x = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
+      sum += taps_w[c * taps + j] * x;
+    }
+    conv_s[c] = sum * sigmoid_f(sum);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int h = warp; h < 2 * kv_heads; h += warps) {   // q heads then k heads
+    float squares = 0.0f;
+    for (int d = lane; d < dim; d += 32) squares += conv_s[h * dim + d] * conv_s[h * dim + d];
+    squares = warp_sum(squares);
+    if (lane == 0) inv_s[h] = (1.0f / sqrtf(squares + unit_eps)) * (h < kv_heads ? q_scale : 1.0f);
+  }
+  __syncthreads();
+  const int width = 2 * qk + heads * vdim + heads + heads * dim;
+  float* out = prep + (size_t)t * width;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) out[c] = c < 2 * qk ? conv_s[c] * inv_s[c / dim] : conv_s[c];
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) out[channels + h] = sigmoid_f(to_float(rows[(size_t)t * row_stride + beta_offset + h]));
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    const float rate = expf(a_log[i / dim]);
+    out[channels + heads + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * heads * dim + i]) + dt_bias[i]));
+  }
+}
+
+template <typename T>
+__global__ void delta_conv_state_kernel(const T* __restrict__ rows, int row_stride, float* __restrict__ state, long long state_stride, long long conv_offset,
+                                        const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int channels, int taps) {
+  const int entry = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int first = seq_starts[entry], count = seq_starts[entry + 1] - first;
+  float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
+  float keep[kDeltaMaxTaps];
+  for (int i = 0; i < taps - 1; ++i) {
+    const int back = count - (taps - 1) + i;
+    keep[i] = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
+  }
+  for (int i = 0; i < taps - 1; ++i) conv_state[(size_t)i * channels + c] = keep[i];
+}
+
+// R: key channels per lane (dim <= 8 R).
+template <int R>
+__global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
+                                                                  const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
+                                                                  int heads, int kv_heads, int dim, int vdim) {
+  extern __shared__ float stage_s[];   // two buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta]
+  constexpr int kPadded = kDeltaLanes * R;
+  constexpr int kRow = 3 * kPadded + kDeltaColumns + 1;
+  constexpr int kLoads = (kRow + kDeltaThreads - 1) / kDeltaThreads;
+  const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
+  const int head = blockIdx.x / column_blocks, block = blockIdx.x - head * column_blocks;
+  const int entry = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & (kDeltaLanes - 1), column = block * kDeltaColumns + tid / kDeltaLanes;
+  const bool live = column < vdim;
+  const int first = seq_starts[entry], count = seq_starts[entry + 1] - first;
+  const int kv = head / (heads / kv_heads);
+  const int qk = kv_heads * dim;
+  const int width = 2 * qk + heads * vdim + heads + heads * dim;
+  const size_t matrix = (size_t)R * vdim * kDeltaLanes;
+  float* mine = state + (size_t)state_slots[entry] * state_stride + (size_t)head * matrix;
+
+  // where each word of a staged row comes from in a prep row (-1: padding, reads as zero)
+  int source[kLoads];
+#pragma unroll
+  for (int i = 0; i < kLoads; ++i) {
+    const int w = tid + i * kDeltaThreads;
+    int at = -1;
+    if (w < kPadded) at = w < dim ? kv * dim + w : -1;
+    else if (w < 2 * kPadded) at = w - kPadded < dim ? qk + kv * dim + (w - kPadded) : -1;
+    else if (w < 3 * kPadded) at = w - 2 * kPadded < dim ? 2 * qk + heads * vdim + heads + head * dim + (w - 2 * kPadded) : -1;
+    else if (w < 3 * kPadded + kDeltaColumns) at = block * kDeltaColumns + (w - 3 * kPadded) < vdim ? 2 * qk + head * vdim + block * kDeltaColumns + (w - 3 * kPadded) : -1;
+    else if (w == 3 * kPadded + kDeltaColumns) at = 2 * qk + heads * vdim + head;
+    source[i] = at;
+  }
+  float S[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = live ? mine[((size_t)i * vdim + column) * kDeltaLanes + lane] : 0.0f;
+
+  float fetched[kLoads];
+  auto fetch = [&](int row) {
+    const float* from = prep + (size_t)(first + row) * width;
+#pragma unroll
+    for (int i = 0; i < kLoads; ++i) fetched[i] = source[i] >= 0 ? from[source[i]] : 0.0f;
+  };
+  auto put = [&](int buffer) {
+#pragma unroll
+    for (int i = 0; i < kLoads; ++i)
+      if (tid + i * kDeltaThreads < kRow) stage_s[buffer * kRow + tid + i * kDeltaThreads] = fetched[i];
+  };
+  if (count > 0) {
+    fetch(0);
+    put(0);
+  }
+  __syncthreads();
+  for (int row = 0; row < count; ++row) {
+    const float* cur = stage_s + (row & 1) * kRow;
+    if (row + 1 < count) fetch(row + 1);
+    float reach = 0.0f, read = 0.0f, both = 0.0f;   // k . (g S)_j, q . (g S)_j, q . k  (this lane's share)
+    float kk[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int d = lane + kDeltaLanes * i;
+      const float q = cur[d], k = cur[kPadded + d], g = cur[2 * kPadded + d];
+      S[i] *= g;
+      reach += k * S[i];
+      read += q * S[i];
+      both += q * k;
+      kk[i] = k;
+    }
+#pragma unroll
+    for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1) {
+      reach += __shfl_xor_sync(0xffffffffu, reach, offset);
+      read += __shfl_xor_sync(0xffffffffu, read, offset);
+      both += __shfl_xor_sync(0xffffffffu, both, offset);
+    }
+    const float v = cur[3 * kPadded + (tid / kDeltaLanes)], beta = cur[3 * kPadded + kDeltaColumns];
+    const float u = beta * (v - reach);
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
+    if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
+    if (row + 1 < count) put((row + 1) & 1);
+    __syncthreads();
+  }
+  if (live && count > 0) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) mine[((size_t)i * vdim + column) * kDeltaLanes + lane] = S[i];
+  }
+}
+
+// a warp per (token, head)
+template <typename T>
+__global__ void delta_gate_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, const float* __restrict__ weight, T* __restrict__ out, float eps,
+                                       int vdim, size_t pairs) {
+  const size_t pair = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const float* row = o + pair * vdim;
+  float squares = 0.0f;
+  for (int d = lane; d < vdim; d += 32) squares += row[d] * row[d];
+  const float inv = rsqrtf(warp_sum(squares) / (float)vdim + eps);
+  for (int d = lane; d < vdim; d += 32) out[pair * vdim + d] = from_float<T>(row[d] * inv * weight[d] * sigmoid_f(to_float(gate[pair * vdim + d])));
+}
+
+template <int R>
+static int launch_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
+                             int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+  const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
+  const size_t smem = 2 * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 1) * sizeof(float);
+  delta_rule_kernel<R><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads, kv_heads,
+                                                                                           dim, vdim);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, int beta_offset, const void* a, const float* taps_w, const float* a_log,
+                                   const float* dt_bias, float* state, long long state_stride, long long conv_offset, const int* token_seq, const int* seq_starts,
+                                   const int* state_slots, float* prep, int tokens, int entries, int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps,
+                                   float q_scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (taps < 1 || taps > kDeltaMaxTaps || kv_heads < 1 || heads % kv_heads != 0 || 2 * kv_heads > 64) return (int)cudaErrorInvalidValue;
+  const int channels = 2 * kv_heads * dim + heads * vdim;
+  const size_t smem = (size_t)channels * sizeof(float);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  if (dtype == TLIE_F32)
+    delta_prepare_kernel<float><<<tokens, 128, smem, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, taps_w, a_log, dt_bias, state, state_stride,
+                                                               conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);
+  else
+    delta_prepare_kernel<__nv_bfloat16><<<tokens, 128, smem, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, taps_w, a_log, dt_bias,
+                                                                       state, state_stride, conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim,
+                                                                       vdim, taps, unit_eps, q_scale);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess || taps == 1) return (int)status;
+  const dim3 grid((channels + 127) / 128, entries);
+  if (dtype == TLIE_F32)
+    delta_conv_state_kernel<float><<<grid, 128, 0, stream>>>((const float*)rows, row_stride, state, state_stride, conv_offset, seq_starts, state_slots, channels, taps);
+  else
+    delta_conv_state_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, state, state_stride, conv_offset, seq_starts, state_slots,
+                                                                     channels, taps);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
+                                int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+  if (entries <= 0) return 0;
+  if (dim < 1 || dim > 256 || kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
+  const int r = (dim + kDeltaLanes - 1) / kDeltaLanes;
+#define TLIE_DELTA(R) \
+  if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream)
+  TLIE_DELTA(4);
+  TLIE_DELTA(8);
+  TLIE_DELTA(12);
+  TLIE_DELTA(16);
+  TLIE_DELTA(24);
+  TLIE_DELTA(32);
+#undef TLIE_DELTA
+  return (int)cudaErrorInvalidValue;
+}
+
+TLIE_EXPORT int tlie_delta_gate_norm(int dtype, const float* o, const void* gate, const float* weight, void* out, float eps, int tokens, int heads, int vdim,
+                                     cudaStream_t stream) {
+  const size_t pairs = (size_t)tokens * heads;
+  if (pairs == 0) return 0;
+  const int blocks = (int)((pairs + 3) / 4);
+  if (dtype == TLIE_F32)
+    delta_gate_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, weight, (float*)out, eps, vdim, pairs);
+  else
+    delta_gate_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, weight, (__nv_bfloat16*)out, eps, vdim, pairs);
+  return (int)cudaGetLastError();
+}

@@ -1,4 +1,4 @@
-// True 32-bit matrix product for the float32 path: out[M, N] = x[M, K] . w[N, K]^T.
+// True 32-bit matrix product for the float32 path: out[M, N] = x[M, K] . w[N, K]^T (rows of x ``lda`` elements apart).
 //
 // The reference's 32-bit model computes each output as one dot product over K in index
 // order (src/model.cpp:53-78).  This kernel keeps that property on the GPU: every output
@@ -13,7 +13,7 @@ constexpr int kTile = 64;
 constexpr int kTileK = 16;
 
 __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                          float* __restrict__ out, int M, int N, int K) {
+                                                          float* __restrict__ out, int M, int N, int K, long long lda) {
   __shared__ float xs[kTileK][kTile + 1];
   __shared__ float ws[kTileK][kTile + 1];
   const int tx = threadIdx.x % 16;
@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restric
       const int gk = k0 + k;
       const int gr = row0 + r;
       const int gc = col0 + r;
-      xs[k][r] = (gr < M && gk < K) ? x[(size_t)gr * K + gk] : 0.0f;
+      xs[k][r] = (gr < M && gk < K) ? x[(size_t)gr * lda + gk] : 0.0f;
       ws[k][r] = (gc < N && gk < K) ? w[(size_t)gc * K + gk] : 0.0f;
     }
     __syncthreads();
@@ -67,11 +67,11 @@ __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restric
 
 using namespace tlie;
 
-TLIE_EXPORT int tlie_gemm_nt_f32(const float* x, const float* w, float* out, int M, int N, int K,
+TLIE_EXPORT int tlie_gemm_nt_f32(const float* x, const float* w, float* out, int M, int N, int K, long long lda,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0) return (int)cudaErrorInvalidValue;
+  if (K <= 0 || lda < K) return (int)cudaErrorInvalidValue;
   dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile);
-  gemm_nt_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K);
+  gemm_nt_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K, lda);
   return (int)cudaGetLastError();
 }

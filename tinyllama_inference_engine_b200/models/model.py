@@ -70,10 +70,10 @@ class DecoderModel:
                 if isinstance(pending, ops.LazyNorm):
                     pending = None   # the residual is complete; this block does not know prepared norms
                 residual, pending = block.forward(residual, pending, ctx, cache)
-            if trace is not None:
+            if trace is not None and block.traced:
                 # the layer's output is the residual with what is still pending on it (a prepared norm means nothing is)
                 complete = residual if pending is None or isinstance(pending, ops.LazyNorm) else residual + pending.float()
-                trace[f"layer{index}.output"] = complete.float().clone()
+                trace[f"layer{len(trace)}.output"] = complete.float().clone()
         if isinstance(pending, ops.LazyNorm):
             return residual, pending
         if pending is not None:

@@ -18,9 +18,10 @@ import torch
 from ..errors import KernelError
 from .build import build_library, load_library
 
-CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "rowwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
 RECURRENT_SOURCES = ["recurrent.cu"]              # compiled when a model with a recurrent mixer is first stepped
 MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with a distance bias, mixed heads or an output gate
+DELTA_RULE_SOURCES = ["delta_rule.cu"]             # likewise for the gated delta rule
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 
@@ -37,7 +38,7 @@ def core():
 def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
     return [build_library("tlie_core", CORE_SOURCES), build_library("tlie_recurrent", RECURRENT_SOURCES),
-            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES)] + fast.build_all()
+            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library("tlie_delta_rule", DELTA_RULE_SOURCES)] + fast.build_all()
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -188,9 +189,80 @@ def silu_mul(gate_up, out) -> None:
     _check(core().tlie_silu_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), _stream()), "silu_mul")
 
 
+def add_row_vector(residual, delta, vector) -> None:
+    """residual[t] += delta[t] (if given) + vector, in 32-bit: a learned vector joins every row of the stream."""
+    rows, hidden = residual.shape
+    if residual.dtype != torch.float32 or vector.dtype != torch.float32 or vector.numel() != hidden or (delta is not None and delta.shape != residual.shape):
+        raise KernelError("add_row_vector: a 32-bit residual [rows, hidden], a 32-bit vector [hidden], a delta of the residual's shape", code="invalid_shape")
+    _check(core().tlie_add_row_vector(_code(delta) if delta is not None else _F32, _ptr(residual), _ptr(delta), _ptr(vector), c_int(rows), c_int(hidden), _stream()),
+           "add_row_vector")
+
+
+def complete_and_round(residual, delta, out) -> None:
+    """residual += delta (if given), then out = the residual in ``out``'s dtype: the finished stream as a product's operand."""
+    if residual.dtype != torch.float32 or out.shape != residual.shape or (delta is not None and (delta.shape != residual.shape or delta.dtype != out.dtype)):
+        raise KernelError("complete_and_round: the residual is 32-bit; delta and out have its shape and one dtype", code="invalid_shape")
+    _check(core().tlie_complete_and_round(_code(out), _ptr(residual), _ptr(delta), _ptr(out), c_longlong(residual.numel()), _stream()), "complete_and_round")
+
+
+def clamped_gate_mul(gate_up, out, limit: float, alpha: float, shift: float) -> None:
+    """out = g sigmoid(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit), for gate_up = [gate | up]."""
+    rows, inter = out.shape
+    if gate_up.shape != (rows, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("clamped_gate_mul: gate_up must be [rows, 2 * inter] of the output's dtype", code="invalid_shape")
+    _check(core().tlie_clamped_gate_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), c_float(limit), c_float(alpha), c_float(shift), _stream()),
+           "clamped_gate_mul")
+
+
+def scale_rows(x, factor: float) -> None:
+    """x *= factor in place (32-bit)."""
+    if x.dtype != torch.float32:
+        raise KernelError("scale_rows takes a 32-bit tensor", code="invalid_dtype")
+    _check(core().tlie_scale_rows(_ptr(x), c_float(factor), c_longlong(x.numel()), _stream()), "scale_rows")
+
+
+def gather_gated(z, table, ids, out, offset: int) -> None:
+    """out[t, d] = gelu_tanh(z[t, d]) * table[ids[t], offset + d]: a slice of a second token table, gated."""
+    rows, dim = out.shape
+    if z.shape != out.shape or z.dtype != out.dtype or table.dtype != out.dtype or table.dim() != 2:
+        raise KernelError("gather_gated: z, out [rows, dim] and the table are of one dtype", code="invalid_shape")
+    _check(core().tlie_gather_gated(_code(out), _ptr(z), _ptr(table), _i32(ids, "ids"), _ptr(out), c_int(rows), c_int(dim), c_int(table.shape[1]), c_int(offset),
+                                    c_int(table.shape[0]), _stream()), "gather_gated")
+
+
+def unit_norm_add(residual, y, weight, eps: float) -> None:
+    """residual[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight, statistics and sum in 32-bit."""
+    rows, hidden = residual.shape
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != hidden or y.shape != residual.shape:
+        raise KernelError("unit_norm_add: a 32-bit residual and weight, y of the residual's shape", code="invalid_shape")
+    _check(core().tlie_unit_norm_add(_code(y), _ptr(residual), _ptr(y), _ptr(weight), c_float(eps), c_int(rows), c_int(hidden), _stream()), "unit_norm_add")
+
+
 # --- matrix products --------------------------------------------------------------------
+HEAD_LINEAR_LIBRARY_ROWS = 64    # from this many bfloat16 rows on the per-head product is one batched library product
+
+
+def head_linear(x, weight, out) -> None:
+    """out[t, h, :] = weight[h] . x[t, h, :] for every head: x [T, H, K] and out [T, H, N] may be views with strides of their own
+    (last axis contiguous), weight [H, N, K] contiguous.  32-bit sums, ascending k (a row's bits depend on the row alone) in the
+    engine's own kernel; bfloat16 steps of many rows go to the library's batched product, as the other products of their size do."""
+    rows, heads, k_in = x.shape
+    n_out = weight.shape[1]
+    if weight.shape != (heads, n_out, k_in) or out.shape != (rows, heads, n_out) or x.stride(2) != 1 or out.stride(2) != 1 or not weight.is_contiguous():
+        raise KernelError("head_linear: x [T, H, K], weight [H, N, K], out [T, H, N] with contiguous last axes", code="invalid_shape")
+    if x.dtype != weight.dtype or out.dtype != x.dtype:
+        raise KernelError("head_linear: one dtype for x, weight and out", code="invalid_dtype")
+    if not x.is_cuda:
+        raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
+    if x.dtype == torch.bfloat16 and rows >= HEAD_LINEAR_LIBRARY_ROWS:
+        torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    _check(core().tlie_head_linear(_code(x), c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_longlong(x.stride(1)), _ptr(weight), c_void_p(out.data_ptr()),
+                                   c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(rows), c_int(heads), c_int(n_out), c_int(k_in), _stream()), "head_linear")
+
+
 def linear(x, weight, out) -> None:
-    """out[M, N] = x[M, K] . weight[N, K]^T in the tensors' dtype (32-bit accumulation)."""
+    """out[M, N] = x[M, K] . weight[N, K]^T in the tensors' dtype (32-bit accumulation); ``x`` may be a run of columns of wider rows."""
     M, K = x.shape
     N = weight.shape[0]
     if weight.shape[1] != K or out.shape != (M, N):
@@ -198,7 +270,9 @@ def linear(x, weight, out) -> None:
     if x.dtype == torch.float32:
         if weight.dtype != torch.float32 or out.dtype != torch.float32:
             raise KernelError("linear: the 32-bit path takes 32-bit weights and outputs", code="invalid_dtype")
-        _check(core().tlie_gemm_nt_f32(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), _stream()), "gemm_nt_f32")
+        if not x.is_cuda or x.stride(1) != 1:
+            raise KernelError("linear: x must be on a CUDA device with contiguous rows")
+        _check(core().tlie_gemm_nt_f32(c_void_p(x.data_ptr()), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)), _stream()), "gemm_nt_f32")
         return
     fast.linear_bf16(x, weight, out)
 
@@ -419,6 +493,63 @@ def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_ro
                                         _i32(state_slots, "state_slots"), _ptr(out), c_int(entries), c_int(width), c_int(runs), _stream()), "mingru_scan")
 
 
+DELTA_LANES = 8   # lanes that share a column of the delta rule's state: the matrix is stored [ceil(dim / 8)][vdim][8] per head
+
+
+def delta_rule_library():
+    return load_library("tlie_delta_rule", DELTA_RULE_SOURCES)
+
+
+def delta_state_words(heads: int, dim: int, vdim: int, channels: int, taps: int) -> tuple[int, int]:
+    """(words of a request's delta-rule state, where the convolution's inputs start in it): the heads' matrices, then taps - 1 rows of inputs."""
+    matrices = heads * (-(-dim // DELTA_LANES)) * DELTA_LANES * vdim
+    return matrices + (taps - 1) * channels, matrices
+
+
+def delta_prepare(rows, beta_offset: int, decay_in, taps, a_log, dt_bias, state, conv_offset: int, ctx, prep, heads: int, kv_heads: int, dim: int, vdim: int,
+                  unit_eps: float, q_scale: float) -> None:
+    """What the delta rule's recurrence reads, per token, in 32-bit: ``prep[t] = [q | k | v | beta | decay]``.
+
+    ``rows`` [T, >= channels + heads] starts with the products for q, k (``kv_heads * dim`` each) and v (``heads * vdim``) and holds the
+    beta pre-activations from ``beta_offset``.  q, k, v pass a causal convolution over time per channel (``taps`` [channels, n], last
+    column the current token's; the inputs before an entry's first row are read from the request's state at ``conv_offset``) and silu;
+    q and k become unit vectors per head (``unit_eps`` inside the root), q times ``q_scale``; beta = sigmoid; decay =
+    exp(-exp(a_log[h]) softplus(decay_in + dt_bias)) per head and key channel.  Afterwards the state's convolution inputs are moved on."""
+    tokens = rows.shape[0]
+    channels = 2 * kv_heads * dim + heads * vdim
+    width = channels + heads + heads * dim
+    if prep.shape != (tokens, width) or prep.dtype != torch.float32 or state.dtype != torch.float32 or state.dim() != 2:
+        raise KernelError("delta_prepare: prep is 32-bit [rows, 2 G dim + H vdim + H + H dim], the state 32-bit [slots, words]", code="invalid_shape")
+    if decay_in.shape != (tokens, heads * dim) or decay_in.dtype != rows.dtype or tuple(taps.shape)[0] != channels or taps.dtype != torch.float32:
+        raise KernelError("delta_prepare: decay_in [rows, H dim] of the rows' dtype, taps 32-bit [channels, n]", code="invalid_shape")
+    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != heads or dt_bias.numel() != heads * dim or rows.stride(1) != 1:
+        raise KernelError("delta_prepare: a_log [H] and dt_bias [H dim] are 32-bit", code="invalid_shape")
+    _check(delta_rule_library().tlie_delta_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), c_int(beta_offset), _ptr(decay_in), _ptr(taps), _ptr(a_log),
+                                                   _ptr(dt_bias), _ptr(state), c_longlong(state.shape[1]), c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"),
+                                                   _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), _ptr(prep), c_int(tokens), c_int(ctx.num_seqs),
+                                                   c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(taps.shape[1]), c_float(unit_eps), c_float(q_scale), _stream()),
+           "delta_prepare")
+
+
+def delta_rule(prep, state, ctx, out, heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+    """The gated delta rule over every entry's rows in order, from and into the entries' state slots: per head
+    S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  ``out`` is 32-bit [T, heads * vdim]."""
+    tokens = prep.shape[0]
+    if out.shape != (tokens, heads * vdim) or out.dtype != torch.float32 or prep.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("delta_rule: prep, state and out [rows, H vdim] are 32-bit", code="invalid_shape")
+    _check(delta_rule_library().tlie_delta_rule(_ptr(prep), _ptr(state), c_longlong(state.shape[1]), _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"),
+                                                _ptr(out), c_int(ctx.num_seqs), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _stream()), "delta_rule")
+
+
+def delta_gate_norm(o, gate, weight, out, eps: float, heads: int, vdim: int) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]) per head (``weight`` [vdim] shared by the heads)."""
+    tokens = o.shape[0]
+    if o.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != vdim or gate.shape != (tokens, heads * vdim) or out.shape != gate.shape or gate.dtype != out.dtype:
+        raise KernelError("delta_gate_norm: o 32-bit [rows, H vdim], weight 32-bit [vdim], gate and out of one dtype and o's shape", code="invalid_shape")
+    _check(delta_rule_library().tlie_delta_gate_norm(_code(out), _ptr(o), _ptr(gate), _ptr(weight), _ptr(out), c_float(eps), c_int(tokens), c_int(heads), c_int(vdim), _stream()),
+           "delta_gate_norm")
+
+
 # --- attention with mixed heads --------------------------------------------------------------
 def mixed_attention():
     return load_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES)
@@ -438,6 +569,45 @@ def _plane_pointers(cache, heads: int, key_dim: int, value_dim: int):
     return k_pages, _ptr(k_pages), heads * cache.page_size * key_dim, _ptr(v_pages), heads * cache.page_size * value_dim
 
 
+def normed_store(rows, k_offset: int, v_offset: int, positions, token_seq, cache, heads: int, kv_heads: int, key_dim: int, value_dim: int, eps: float,
+                 q_weight=None, k_weight=None) -> None:
+    """Divide every query head (in place) and key head of ``rows`` by its root mean square (``eps`` inside the root; times a 32-bit
+    weight [key_dim] if given); write the normalised keys into the key plane of the tokens' pages and the ``kv_heads * value_dim``
+    columns from ``v_offset`` into the value plane as they are (``v_offset == k_offset``: the values are the keys before the norm)."""
+    pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
+    if pages.dtype != rows.dtype:
+        raise KernelError("normed_store: pages and rows differ in dtype", code="invalid_dtype")
+    table = cache.block_table
+    _check(mixed_attention().tlie_normed_store(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(k_offset), c_int(v_offset), _ptr(q_weight), _ptr(k_weight), c_float(eps),
+                                               _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"), c_int(table.shape[1]), k_ptr,
+                                               c_longlong(k_stride), v_ptr, c_longlong(v_stride), c_int(rows.shape[0]), c_int(heads), c_int(kv_heads), c_int(key_dim),
+                                               c_int(value_dim), c_int(cache.page_size), c_int(1 if cache.writes else 0), _stream()), "normed_store")
+
+
+def _latent_plane(cache, width: int):
+    pages = cache.pages
+    if pages is None or pages.dim() != 5 or tuple(pages.shape[1:]) != (1, 1, cache.page_size, width) or not pages.is_contiguous():
+        raise KernelError("latent attention pages must be contiguous [pages, 1, 1, page size, rank + rot]", code="invalid_shape")
+    return pages
+
+
+def latent_store(rows, latent_offset: int, weight, eps: float, inv_freq, rot_dims: int, positions, token_seq, cache, queries, heads: int, plain: int, rot: int, rank: int) -> None:
+    """Latent attention's cache write and rotation: ``rows[:, latent_offset:]`` = [rank | rot] becomes [rms-normed latent (32-bit ``weight``) |
+    rotated shared key part] in the token's cache row; the ``rot`` columns behind the ``plain`` ones of every query head are rotated into
+    ``queries`` [T, heads * (rank + rot)], behind each head's first ``rank`` columns (which are left alone).
+    Pairs (2i, 2i + 1) of the first ``rot_dims`` columns turn by position * inv_freq[i]."""
+    pages = _latent_plane(cache, rank + rot)
+    if queries.shape != (rows.shape[0], heads * (rank + rot)) or queries.dtype != rows.dtype:
+        raise KernelError("latent_store: queries must be [rows, heads * (rank + rot)] of the rows' dtype", code="invalid_shape")
+    if pages.dtype != rows.dtype or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2 or weight.dtype != torch.float32 or weight.numel() != rank:
+        raise KernelError("latent_store: pages of the rows' dtype; inv_freq [rot_dims / 2] and weight [rank] 32-bit", code="invalid_shape")
+    table = cache.block_table
+    _check(mixed_attention().tlie_latent_store(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(latent_offset), _ptr(weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims),
+                                               _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"), c_int(table.shape[1]), _ptr(pages),
+                                               c_longlong(cache.page_size * (rank + rot)), c_int(rows.shape[0]), c_int(heads), c_int(plain), c_int(rot), c_int(rank),
+                                               c_int(cache.page_size), c_int(1 if cache.writes else 0), _ptr(queries), _stream()), "latent_store")
+
+
 def store_kv_planes(rows, k_offset: int, v_offset: int, positions, token_seq, cache, kv_heads: int, key_dim: int, value_dim: int) -> None:
     """Copy every token's keys (``kv_heads * key_dim`` columns of ``rows`` from ``k_offset``) and values (from ``v_offset``) into the
     pages its request holds for its position.  ``cache``: the layer's ``LayerCache`` (one tensor of two equal planes, or a tensor per plane)."""
@@ -452,7 +622,8 @@ def store_kv_planes(rows, k_offset: int, v_offset: int, positions, token_seq, ca
 
 
 def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
-                          window: int, scale: float, batch=None, folded_slopes=None) -> None:
+                          window: int, scale: float, batch=None, folded_slopes=None, keep_first: int = 0, gate_per_head: bool = False, sinks=None,
+                          values_in_keys: bool = False) -> None:
     """Attention over the paged keys with a distance bias, the heads' scores mixed before the softmax, and an output gate.
 
     ``rows`` [T, >= heads * key_dim]: each row starts with its query heads; ``gate_offset`` (>= 0) names the column where
@@ -460,18 +631,32 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     head g at position i for key j: (q . k) * scale - slopes[g] * (i - j) (``slopes`` 32-bit [heads] or None); head h then sees
     sum_g mix[h, g] score_g (``mix`` 32-bit [heads, heads] or None); keys with 0 <= i - j (< window if window > 0) are visible.
     ``batch``: the step's context, from which a faster kernel is chosen where one fits; ``folded_slopes``: ``fast.folded_slopes(slopes, mix)``
-    if the caller keeps it (it is worked out here otherwise)."""
+    if the caller keeps it (it is worked out here otherwise).  ``keep_first``: with a window, the keys at positions below it stay visible.
+    ``gate_per_head``: the gate is ``heads`` columns, one per head.  ``sinks`` (32-bit [heads]): exp(sink_h) joins the softmax's denominator.
+    ``values_in_keys``: the cache has one plane of one key/value head whose rows are the keys and whose first ``value_dim`` columns are the values."""
     tokens = rows.shape[0]
     if heads % kv_heads != 0 or out.shape != (tokens, heads * value_dim) or out.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: out must be [rows, heads * value_dim] of the rows' dtype, heads a multiple of kv heads", code="invalid_shape")
     for name, tensor, count in (("slopes", slopes, heads), ("mix", mix, heads * heads)):
         if tensor is not None and (tensor.dtype != torch.float32 or tensor.numel() != count):
             raise KernelError(f"mixed_heads_attention: {name} must be 32-bit with {count} elements", code="invalid_shape")
-    pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != heads):
+        raise KernelError("mixed_heads_attention: sinks must be 32-bit with one element per head", code="invalid_shape")
+    v_row_stride = value_dim
+    if values_in_keys:
+        if kv_heads != 1 or value_dim > key_dim:
+            raise KernelError("mixed_heads_attention: values inside the keys need one key/value head and value_dim <= key_dim", code="invalid_shape")
+        pages = _latent_plane(cache, key_dim)
+        k_ptr = v_ptr = _ptr(pages)
+        k_stride = v_stride = cache.page_size * key_dim
+        v_row_stride = key_dim
+    else:
+        pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
     if pages.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: pages and rows differ in dtype", code="invalid_dtype")
     table = cache.block_table
-    if rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset):
+    plain_options = keep_first == 0 and not gate_per_head and sinks is None and not values_in_keys   # what the tensor-core kernels know
+    if plain_options and rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset):
         folded = folded_slopes if folded_slopes is not None else fast.folded_slopes(slopes, mix)
         fast.mixed_prefill(rows, gate_offset, batch, table, (k_ptr, k_stride, v_ptr, v_stride), folded, mix, out, heads, kv_heads, key_dim, value_dim,
                            cache.page_size, window, scale)
@@ -479,9 +664,9 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     # few rows over long contexts (decode steps): every row's keys are dealt to several CTAs
     splits, partial = 1, None
     if batch is not None and tokens * 2 <= fast.sm_count():
-        reach = min(window, batch.max_seq_len) if window > 0 else batch.max_seq_len
+        reach = min(window + keep_first, batch.max_seq_len) if window > 0 else batch.max_seq_len
         splits = max(1, min(2 * fast.sm_count() // tokens, -(-reach // 32), 64))   # down to one tile of 32 keys per CTA
-        if fast.mixed_decode_takes(rows, heads, kv_heads, key_dim, value_dim, gate_offset, mix is not None):
+        if plain_options and fast.mixed_decode_takes(rows, heads, kv_heads, key_dim, value_dim, gate_offset, mix is not None):
             fast.mixed_decode(rows, gate_offset, positions, token_seq, table, (k_ptr, k_stride, v_ptr, v_stride), slopes, mix, out, heads, kv_heads, key_dim,
                               value_dim, cache.page_size, window, scale, splits)
             return
@@ -490,7 +675,8 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     _check(mixed_attention().tlie_mixed_heads_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr,
                                                         c_longlong(v_stride), _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"),
                                                         c_int(table.shape[1]), _ptr(slopes), _ptr(mix), _ptr(out), c_int(tokens), c_int(heads), c_int(kv_heads),
-                                                        c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), c_int(splits), _ptr(partial), _stream()),
+                                                        c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), c_int(splits), _ptr(partial),
+                                                        c_int(keep_first if window > 0 else 0), c_int(1 if gate_per_head else 0), _ptr(sinks), c_int(v_row_stride), _stream()),
            "mixed_heads_attention")
 
 

@@ -1,7 +1,9 @@
-"""Attention over the paged cache: grouped-query attention with a position encoding, and attention whose heads are biased by
-distance, mixed before the softmax and gated after it."""
+"""Attention over the paged cache: grouped-query attention with a position encoding; attention whose heads are biased by
+distance, mixed before the softmax and gated after it; attention with normalised queries and keys under a window that keeps
+the first tokens; and latent attention, which caches one small vector per token for all heads."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -172,5 +174,184 @@ class MixedHeadsAttention(Mixer):
         return out
 
 
+class NormedKeyAttention(Mixer):
+    """Grouped heads without positions: queries and keys are divided by their root mean square per head before the product.
+
+    score = (q^ . k^) * scale with x^ = x / sqrt(mean(x^2) + eps); query position i sees key j if j <= i and (i - j < window or
+    j < keep_first) (``window`` 0: every earlier key); an ordinary softmax; head h's output is multiplied by sigmoid((W_g x)_h), one
+    number per head, if ``head_gate``; out = W_o concat(heads).  With ``values`` = "keys" the values are the keys as projected,
+    before the norm, and there is no value projection (then value_dim = key_dim); with "projection" there is ``<prefix>.v``.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``key_dim``, ``value_dim``, ``scale``, ``eps``, ``window``, ``keep_first``,
+    ``values``, ``head_gate``.  tensors: ``<prefix>.q`` [heads * key_dim, hidden], ``<prefix>.k`` [kv * key_dim, hidden], ``<prefix>.v``
+    [kv * value_dim, hidden] (if projected), ``<prefix>.g`` [heads, hidden] (if gated), ``<prefix>.o`` [hidden, heads * value_dim].
+    The cache holds two planes per token: the normalised keys and the values; a window group keeps the pages of the first
+    ``keep_first`` tokens.  Norms, scores, softmax and the gate are 32-bit.
+    """
+
+    capturable = True
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+    prepares_next_norm = True
+
+    @classmethod
+    def _sizes(cls, spec: PartSpec) -> tuple[int, int, int, int, int]:
+        return int(spec["hidden_size"]), int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["key_dim"]), int(spec["value_dim"])
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden, heads, kv, key_dim, value_dim = cls._sizes(spec)
+        std = hidden ** -0.5
+        specs = [TensorSpec(f"{prefix}.q", (heads * key_dim, hidden), std=std), TensorSpec(f"{prefix}.k", (kv * key_dim, hidden), std=std)]
+        if spec.get("values", "projection") != "keys":
+            specs.append(TensorSpec(f"{prefix}.v", (kv * value_dim, hidden), std=std))
+        if spec.get("head_gate"):
+            specs.append(TensorSpec(f"{prefix}.g", (heads, hidden), std=std))
+        return specs + [TensorSpec(f"{prefix}.o", (hidden, heads * value_dim), std=(heads * value_dim) ** -0.5)]
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        _, _, kv, key_dim, value_dim = cls._sizes(spec)
+        window = int(spec.get("window", 0) or 0)
+        return CacheNeed("pages", window=window, planes=((kv, key_dim), (kv, value_dim)), keep_first=int(spec.get("keep_first", 0) or 0) if window > 0 else 0)
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden, self.heads, self.kv_heads, self.key_dim, self.value_dim = self._sizes(spec)
+        self.window = int(spec.get("window", 0) or 0)
+        self.keep_first = int(spec.get("keep_first", 0) or 0)
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        self.values_are_keys = spec.get("values", "projection") == "keys"
+        if self.values_are_keys and self.value_dim != self.key_dim:
+            from ..errors import ConfigError
+
+            raise ConfigError(f"{prefix}: values that are the keys have the keys' width ({self.key_dim}), not {self.value_dim}")
+        dtype = runtime.dtype
+        stacked = [weights.get(f"{prefix}.q", dtype), weights.get(f"{prefix}.k", dtype)]
+        self.k_offset = self.heads * self.key_dim
+        width = self.k_offset + self.kv_heads * self.key_dim
+        self.v_offset = self.k_offset
+        if not self.values_are_keys:
+            self.v_offset = width
+            stacked.append(weights.get(f"{prefix}.v", dtype))
+            width += self.kv_heads * self.value_dim
+        self.gate_offset = -1
+        if spec.get("head_gate"):
+            self.gate_offset = width
+            stacked.append(weights.get(f"{prefix}.g", dtype))
+        self.w_in = torch.cat(stacked, dim=0).contiguous()
+        self.w_o = weights.get(f"{prefix}.o", dtype).contiguous()
+
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_o)
+
+    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
+        ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
+        rows = ws.get("qk_gate", tokens, self.w_in.shape[0], dtype)
+        if isinstance(x, ops.LazyNorm):
+            ops.norm_linear(x, self.w_in, rows)
+        else:
+            ops.linear(x, self.w_in, rows)
+        ops.normed_store(rows, self.k_offset, self.v_offset, ctx.positions, ctx.token_seq, cache, self.heads, self.kv_heads, self.key_dim, self.value_dim, self.eps)
+        mixed = ws.get("attention", tokens, self.heads * self.value_dim, dtype)
+        ops.mixed_heads_attention(rows, self.gate_offset, ctx.positions, ctx.token_seq, cache, None, None, mixed, self.heads, self.kv_heads, self.key_dim,
+                                  self.value_dim, self.window, self.scale, batch=ctx, keep_first=self.keep_first, gate_per_head=True)
+        if accumulate_into is not None:
+            ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
+            return None
+        out = ws.get("mixer_out", tokens, self.hidden, dtype)
+        ops.linear(mixed, self.w_o, out)
+        return out
+
+
+class LatentAttention(Mixer):
+    """Attention whose keys and values are expanded from one latent vector per token, with a rotated key part shared by all heads
+    and, optionally, a sink in the softmax.
+
+    Per token: q = W_q x, head by head [plain | rot]; W_dkv x = [rank | rot]; the latent c is the first ``rank`` columns under an RMS norm
+    with a weight, the last ``rot`` columns are one key part for every head, rotated by position like the queries' rot parts (pairs
+    (2i, 2i + 1) of the first ``rot_dims`` columns by angle position * base^(-2i / rot_dims)).  Head h has keys [W_uk,h c | shared part]
+    and values W_uv,h c; causal; softmax whose denominator also holds exp(sink_h) if ``sink``; out = W_o concat(heads).
+
+    Only [c | rotated part] is cached (one plane, one head, rank + rot wide).  The products with W_uk and W_uv are moved across the
+    attention: q~_h = W_uk,h^T q_plain,h, so that the score is [q~_h | q_rot,h] . [c_j | rot_j] and head h's weighted sum of latents,
+    sum_j p_j c_j, is multiplied by W_uv,h afterwards.  All heads then read the same cached rows: attention with one key/value
+    head whose values are the first ``rank`` columns of its keys.
+
+    params: ``hidden_size``, ``num_heads``, ``plain_dim``, ``rot_dim``, ``value_dim``, ``rank``, ``scale``, ``eps``, ``rot_dims``, ``rot_base``,
+    ``sink``.  tensors: ``<prefix>.q`` [heads * (plain + rot), hidden], ``<prefix>.dkv`` [rank + rot, hidden], ``<prefix>.dkv.norm`` [rank],
+    ``<prefix>.uk`` [heads * plain, rank], ``<prefix>.uv`` [heads * value_dim, rank], ``<prefix>.sink`` [heads], ``<prefix>.o`` [hidden, heads * value_dim].
+    """
+
+    capturable = True
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+    prepares_next_norm = True
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden, heads, plain, rot, vdim, rank = (int(spec[k]) for k in ("hidden_size", "num_heads", "plain_dim", "rot_dim", "value_dim", "rank"))
+        std = hidden ** -0.5
+        specs = [TensorSpec(f"{prefix}.q", (heads * (plain + rot), hidden), std=std), TensorSpec(f"{prefix}.dkv", (rank + rot, hidden), std=std),
+                 TensorSpec(f"{prefix}.dkv.norm", (rank,), init="norm", std=0.1), TensorSpec(f"{prefix}.uk", (heads * plain, rank), std=rank ** -0.5),
+                 TensorSpec(f"{prefix}.uv", (heads * vdim, rank), std=rank ** -0.5)]
+        if spec.get("sink"):
+            specs.append(TensorSpec(f"{prefix}.sink", (heads,), std=1.0))
+        return specs + [TensorSpec(f"{prefix}.o", (hidden, heads * vdim), std=(heads * vdim) ** -0.5)]
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        return CacheNeed("pages", planes=((1, int(spec["rank"]) + int(spec["rot_dim"])),))
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden, self.heads, self.plain, self.rot, self.vdim, self.rank = (int(spec[k]) for k in ("hidden_size", "num_heads", "plain_dim", "rot_dim", "value_dim", "rank"))
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        self.rot_dims = int(spec["rot_dims"])
+        dtype = runtime.dtype
+        self.w_in = torch.cat([weights.get(f"{prefix}.q", dtype), weights.get(f"{prefix}.dkv", dtype)], dim=0).contiguous()
+        self.latent_offset = self.heads * (self.plain + self.rot)
+        self.latent_weight = weights.get(f"{prefix}.dkv.norm", torch.float32).contiguous()
+        # W_uk per head, transposed: [heads, rank, plain], the operand of q~ = W_uk^T q; W_uv per head [heads, vdim, rank]
+        self.w_uk_t = weights.get(f"{prefix}.uk", dtype).view(self.heads, self.plain, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = weights.get(f"{prefix}.uv", dtype).view(self.heads, self.vdim, self.rank).contiguous()
+        self.sinks = weights.get(f"{prefix}.sink", torch.float32).contiguous() if spec.get("sink") else None
+        self.w_o = weights.get(f"{prefix}.o", dtype).contiguous()
+        # frequencies in 64-bit, rounded once: the angle is float(position) * frequency in 32-bit inside the kernel
+        exponent = -2.0 * np.arange(self.rot_dims // 2, dtype=np.float64) / float(self.rot_dims)
+        self.inv_freq = torch.from_numpy(np.power(float(spec["rot_base"]), exponent).astype(np.float32)).to(runtime.device)
+
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_o)
+
+    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
+        ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
+        rows = ws.get("latent_in", tokens, self.w_in.shape[0], dtype)
+        if isinstance(x, ops.LazyNorm):
+            ops.norm_linear(x, self.w_in, rows)
+        else:
+            ops.linear(x, self.w_in, rows)
+        width = self.rank + self.rot
+        flat_queries = ws.get("latent_queries", tokens, self.heads * width, dtype)
+        ops.latent_store(rows, self.latent_offset, self.latent_weight, self.eps, self.inv_freq, self.rot_dims, ctx.positions, ctx.token_seq, cache, flat_queries,
+                         self.heads, self.plain, self.rot, self.rank)
+        queries = flat_queries.view(tokens, self.heads, width)
+        per_head = rows[:, : self.latent_offset].view(tokens, self.heads, self.plain + self.rot)
+        ops.head_linear(per_head[:, :, : self.plain], self.w_uk_t, queries[:, :, : self.rank])
+        summed = ws.get("latent_sums", tokens, self.heads * self.rank, dtype)
+        ops.mixed_heads_attention(flat_queries, -1, ctx.positions, ctx.token_seq, cache, None, None, summed, self.heads, 1, width,
+                                  self.rank, 0, self.scale, batch=ctx, sinks=self.sinks, values_in_keys=True)
+        mixed = ws.get("attention", tokens, self.heads * self.vdim, dtype)
+        ops.head_linear(summed.view(tokens, self.heads, self.rank), self.w_uv, mixed.view(tokens, self.heads, self.vdim))
+        if accumulate_into is not None:
+            ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
+            return None
+        out = ws.get("mixer_out", tokens, self.hidden, dtype)
+        ops.linear(mixed, self.w_o, out)
+        return out
+
+
 register_part("mixer", "attention", Attention)
 register_part("mixer", "mixed_heads_attention", MixedHeadsAttention)
+register_part("mixer", "normed_key_attention", NormedKeyAttention)
+register_part("mixer", "latent_attention", LatentAttention)

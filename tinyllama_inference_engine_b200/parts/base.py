@@ -43,7 +43,8 @@ from .spec import PartSpec, TensorSpec
 class CacheNeed:
     """What a mixer keeps per request between steps.
 
-    kind "pages": for every cached token (or only the last ``window`` tokens if window > 0) a number of *planes*, each
+    kind "pages": for every cached token (or only the last ``window`` tokens if window > 0, and beside them the first
+    ``keep_first`` tokens of the request) a number of *planes*, each
     ``heads`` vectors of ``width`` elements: ``planes = ((heads, width), ...)``.  Keys and values of ``kv_heads`` heads of
     ``head_dim`` are two equal planes, which is what ``kv_heads`` / ``head_dim`` alone mean; one latent vector per token
     would be a single plane, keys and values of different widths two unequal ones.
@@ -57,6 +58,7 @@ class CacheNeed:
     window: int = 0
     state_shape: tuple[int, ...] = ()
     planes: tuple[tuple[int, int], ...] = ()
+    keep_first: int = 0
 
     def page_planes(self) -> tuple[tuple[int, int], ...]:
         """The planes of a page: as given, or keys and values of ``kv_heads`` x ``head_dim``."""
@@ -69,7 +71,7 @@ class CacheNeed:
         return all(plane == planes[0] for plane in planes)
 
     def group_key(self) -> tuple:
-        return (self.kind, self.page_planes(), self.window, self.state_shape)
+        return (self.kind, self.page_planes(), self.window, self.state_shape, self.keep_first if self.window > 0 else 0)
 
 
 @dataclass
@@ -191,8 +193,19 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenInput(Part):
+    """Something a layer adds to the stream from the token itself (a table row, gated by the stream): ``forward(residual, ctx)``
+    adds into the complete 32-bit ``residual`` in place."""
+
+    category = "token_input"
+
+    def forward(self, residual, ctx) -> None:
+        raise NotImplementedError
+
+
 class Block(Part):
     category = "block"
+    traced = True                  # False: a run of this block is no layer of its own in a trace of layer outputs
     accepts_next_norm = False      # forward(..., next_norm=<Norm>) : the norm that will read this block's result, if known
     first_norm = None              # the norm that reads this block's input first, if it has one: what the block before is told as ``next_norm``
 
@@ -242,7 +255,7 @@ def norm_then_part(norm, part, residual, pending, fused: bool, next_norm, *args)
 
 # --- registry of part classes -------------------------------------------------------------
 _PARTS: dict[tuple[str, str], type] = {}
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "token_input")
 
 
 def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:

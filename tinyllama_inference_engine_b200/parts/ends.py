@@ -85,7 +85,8 @@ class LinearHead(Part):
     embedding table, or None).  With ``tied_to`` the head's own tensor is optional:
     a checkpoint that stores it anyway is read as it is, one that does not makes the
     head alias the embedding table.  The reference refuses tied checkpoints
-    (src/model_config.cpp:72).
+    (src/model_config.cpp:72).  A head whose ``tensor`` is the embedding table's own name is that table.
+    Optional ``scale``: the logits are multiplied by it (32-bit, after the product).
     """
 
     capturable = True
@@ -101,6 +102,7 @@ class LinearHead(Part):
         source = own if not spec.get("tied_to") or weights.has(own) else f"{spec['tied_to']}.weight"
         self.weight = weights.get(source, runtime.dtype).contiguous()
         self.vocab = int(spec["vocab_size"])
+        self.scale = float(spec.get("scale", 1.0) or 1.0)
 
     def forward(self, normed_rows):
         """``normed_rows`` is the normalised hidden state of the wanted rows, or an ops.LazyNorm of it."""
@@ -110,6 +112,8 @@ class LinearHead(Part):
             ops.norm_linear(normed_rows, self.weight, logits)
         else:
             ops.linear(normed_rows, self.weight, logits)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
         return logits
 
 

@@ -12,7 +12,9 @@ from .spec import PartSpec, TensorSpec
 class GatedMLP(FeedForward):
     """down( act(gate(x)) * up(x) ) with act = SiLU (src/model.cpp:187-203, src/operators.cpp:148-164).
 
-    params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu").
+    params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu", or "clamped_sigmoid": with g = min(gate, limit) and
+    u = clamp(up, -limit, limit) the product is g * sigmoid(alpha * g) * (u + shift); params ``limit``, ``alpha``, ``shift``),
+    optional ``names`` = (gate, up, down) tensor suffixes in full.
     tensors: ``<prefix>.{gate,up}_proj.weight [inter, hidden]``,
     ``<prefix>.down_proj.weight [hidden, inter]``.  gate and up are stacked at load
     time into one ``[2 * inter, hidden]`` product; the activation and the product with
@@ -25,23 +27,31 @@ class GatedMLP(FeedForward):
     prepares_next_norm = True
 
     @classmethod
+    def _names(cls, spec: PartSpec, prefix: str) -> tuple[str, str, str]:
+        gate, up, down = spec.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        return f"{prefix}.{gate}", f"{prefix}.{up}", f"{prefix}.{down}"
+
+    @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         hidden, inter = spec["hidden_size"], spec["intermediate_size"]
-        return [
-            TensorSpec(f"{prefix}.gate_proj.weight", (inter, hidden)),
-            TensorSpec(f"{prefix}.up_proj.weight", (inter, hidden)),
-            TensorSpec(f"{prefix}.down_proj.weight", (hidden, inter)),
-        ]
+        gate, up, down = cls._names(spec, prefix)
+        if spec.get("names"):
+            return [TensorSpec(gate, (inter, hidden), std=hidden ** -0.5), TensorSpec(up, (inter, hidden), std=hidden ** -0.5), TensorSpec(down, (hidden, inter), std=inter ** -0.5)]
+        return [TensorSpec(gate, (inter, hidden)), TensorSpec(up, (inter, hidden)), TensorSpec(down, (hidden, inter))]
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        if spec.get("activation", "silu") != "silu":
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in ("silu", "clamped_sigmoid"):
             raise ConfigError(f"gated_mlp has no activation {spec.get('activation')!r}")
+        if self.activation == "clamped_sigmoid":
+            self.limit, self.alpha, self.shift = float(spec["limit"]), float(spec["alpha"]), float(spec["shift"])
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
         dtype = runtime.dtype
-        self.w_gate_up = torch.cat([weights.get(f"{prefix}.gate_proj.weight", dtype), weights.get(f"{prefix}.up_proj.weight", dtype)], dim=0).contiguous()
-        self.w_down = weights.get(f"{prefix}.down_proj.weight", dtype).contiguous()
+        gate, up, down = self._names(spec, prefix)
+        self.w_gate_up = torch.cat([weights.get(gate, dtype), weights.get(up, dtype)], dim=0).contiguous()
+        self.w_down = weights.get(down, dtype).contiguous()
 
     def adds_to_residual(self, rows: int) -> bool:
         return ops.can_accumulate(rows, self.w_down)
@@ -49,7 +59,15 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         act = ws.get("activated", tokens, self.inter, dtype)
-        if tokens <= ops.fused_rows_limit(dtype, act.device):
+        if self.activation == "clamped_sigmoid":
+            # the stacked product, then the clamps, the gate and the shift in one row-wise kernel (32-bit inside)
+            gate_up = ws.get("gate_up", tokens, 2 * self.inter, dtype)
+            if isinstance(x, ops.LazyNorm):
+                ops.norm_linear(x, self.w_gate_up, gate_up)
+            else:
+                ops.linear(x, self.w_gate_up, gate_up)
+            ops.clamped_gate_mul(gate_up, act, self.limit, self.alpha, self.shift)
+        elif tokens <= ops.fused_rows_limit(dtype, act.device):
             # few rows: the gate is applied in the first product's epilogue, the residual add in the second's
             if isinstance(x, ops.LazyNorm):
                 ops.norm_linear(x, self.w_gate_up, act, gated=True)

@@ -11,7 +11,8 @@ from .spec import PartSpec, TensorSpec
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * weight, eps inside the root (src/operators.cpp:22-45).
 
-    params: ``size``, ``eps``, optional ``suffix`` (what follows the prefix in the tensor's name, ".weight" unless given).
+    params: ``size``, ``eps``, optional ``suffix`` (what follows the prefix in the tensor's name, ".weight" unless given), optional
+    ``offset`` (the weight is stored minus this number: 1.0 for a weight stored around zero; added once, in 32-bit, at load time).
     tensors: ``<prefix><suffix> [size]``.
     The statistics, the scale and the residual sum are 32-bit in both precisions;
     the weight is held in 32-bit (exact for a bfloat16 checkpoint).
@@ -22,6 +23,8 @@ class RMSNorm(Norm):
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        if float(spec.get("offset", 0.0) or 0.0) != 0.0:
+            return [TensorSpec(f"{prefix}{spec.get('suffix', '.weight')}", (spec["size"],), init="matrix", std=0.1)]   # stored around zero
         return [TensorSpec(f"{prefix}{spec.get('suffix', '.weight')}", (spec["size"],), init="norm", std=0.1)]
 
     def __init__(self, spec, prefix, weights, runtime):
@@ -29,6 +32,9 @@ class RMSNorm(Norm):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = weights.get(f"{prefix}{spec.get('suffix', '.weight')}", torch.float32).contiguous()
+        offset = float(spec.get("offset", 0.0) or 0.0)
+        if offset != 0.0:
+            self.weight = (self.weight + offset).contiguous()
 
     def forward(self, residual, delta=None, rows=None, lazy: bool = False):
         """``lazy`` (and nothing to add): hand the norm on to the product that consumes it (ops.LazyNorm)."""

@@ -26,7 +26,7 @@ def random_tensors(expected: Iterable[TensorSpec], seed: int, dtype: torch.dtype
     generator.manual_seed(int(seed))
     tensors: dict[str, torch.Tensor] = {}
     for spec in expected:
-        if spec.optional:
+        if spec.optional or spec.name in tensors:   # a tensor two parts share (a tied head) is drawn once
             continue
         if spec.init == "matrix":
             value = torch.randn(spec.shape, generator=generator, dtype=torch.float32) * spec.std
