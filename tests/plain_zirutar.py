@@ -24,9 +24,9 @@ def gelu_tanh(z):
     return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
-def visible(i: int, j: int, window: int, keep_first: int) -> bool:
-    """Whether query position i sees key position j under a sliding window that keeps the first tokens."""
-    return j <= i and (i - j < window or j < keep_first)
+def visible(i: int, j: int, window, keep_first: int) -> bool:
+    """Whether query position i sees key position j under a sliding window that keeps the first tokens (``window`` None: no window)."""
+    return j <= i and (window is None or i - j < window or j < keep_first)
 
 
 def windowed_attention(h, w, p, sizes, eps):
@@ -34,7 +34,8 @@ def windowed_attention(h, w, p, sizes, eps):
     the first tokens, one output gate per head."""
     T = h.shape[0]
     H, G, dim = sizes["heads"], sizes["kv_heads"], sizes["dim"]
-    window, keep = sizes["mask"]["size"], sizes["mask"]["keep_first"]
+    mask = sizes.get("mask") or {}
+    window, keep = mask.get("size"), mask.get("keep_first", 0)
     q = (h @ w[p + ".q"].T).view(T, H, dim)
     k = (h @ w[p + ".k"].T).view(T, G, dim)
     v = k

@@ -101,8 +101,11 @@ def expected_rows(steps: list[dict], full_logits: dict[str, torch.Tensor]) -> di
     return out
 
 
-def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tensor], atol: float, rtol: float = 0.0) -> float:
-    """Replay the steps through the engine's step function; returns the largest error seen."""
+def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tensor], atol: float, rtol: float = 0.0, over_vocabulary: bool = False) -> float:
+    """Replay the steps through the engine's step function; returns the largest error seen.
+
+    ``over_vocabulary``: a row's error is the root mean square of its differences over the vocabulary (what rounding noise that a
+    model amplifies looks like) instead of its largest difference."""
     from tinyllama_inference_engine_b200.engine.replay import replay_step
 
     expected = expected_rows(steps, full_logits)
@@ -113,6 +116,8 @@ def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tens
             want = expected[step["step"]]
             assert got is not None and got.shape == want.shape, (step["step"], None if got is None else got.shape, want.shape)
             error = (got - want).abs()
+            if over_vocabulary:
+                error = (error * error).mean(dim=1, keepdim=True).sqrt().expand_as(want)
             bound = atol + rtol * want.abs()
             if not bool((error <= bound).all()):
                 row = int((error - bound).max(1).values.argmax())

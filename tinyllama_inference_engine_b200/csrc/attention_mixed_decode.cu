@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(kThreads)
                         long long k_page_stride, const __nv_bfloat16* __restrict__ v_pages, long long v_page_stride, const int* __restrict__ positions,
                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes,
                         const float* __restrict__ mix, __nv_bfloat16* __restrict__ out, int heads, int page_size, int window, float scale,
-                        float* __restrict__ partial) {
+                        float* __restrict__ partial, int keep_first, int gate_per_head) {
   extern __shared__ __align__(16) unsigned char smem[];
   const DecodeSmem at(heads, mix != nullptr);
   long long* k_at = reinterpret_cast<long long*>(smem + at.rows);
@@ -101,17 +101,20 @@ __global__ void __launch_bounds__(kThreads)
     for (int i = 0; i < kVD / 8; ++i) o[u][i][0] = o[u][i][1] = o[u][i][2] = o[u][i][3] = 0.0f;
 
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  // The visible keys are numbered 0, 1, ...: first the ``kept`` keys that stay visible behind the window, then the window's.
+  const int kept = min(keep_first, lo);
+  const int visible = kept + (pos - lo + 1);
   const int splits = gridDim.y;
-  const int tiles = (pos - lo) / kKeys + 1;
+  const int tiles = (visible + kKeys - 1) / kKeys;
   const int tiles_each = (tiles + splits - 1) / splits;
-  const int first_key = lo + blockIdx.y * tiles_each * kKeys;
-  const int last_key = min(pos, first_key + tiles_each * kKeys - 1);
+  const int first_key = blockIdx.y * tiles_each * kKeys;
+  const int last_key = min(visible - 1, first_key + tiles_each * kKeys - 1);
 
   for (int base = first_key; base <= last_key; base += kKeys) {
     const int count = min(kKeys, last_key - base + 1);
     __syncthreads();   // the tile before is done with its rows, keys and values (and, the first time, the queries are in place)
     if (tid < count) {
-      const int key = base + tid;
+      const int key = base + tid < kept ? base + tid : lo + (base + tid - kept);
       const long long page = table[key / page_size];
       const int slot = key % page_size;
       k_at[tid] = page * k_page_stride + (long long)slot * kD;
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(kThreads)
             if (in_group < group) {
               const int h = c * group + in_group;
               float raw = s[j][e] * scale;
-              if (slopes) raw -= slopes[h] * (float)(pos - (base + key));
+              if (slopes) raw -= slopes[h] * (float)(pos - (base + key < kept ? base + key : lo + (base + key - kept)));
               raw_s[h * kKeys + key] = raw;
             }
           }
@@ -259,7 +262,11 @@ __global__ void __launch_bounds__(kThreads)
           mine[h * kVD + d] = a;
           mine[h * kVD + d + 1] = b;
         } else {
-          if (gate_offset >= 0) {
+          if (gate_offset >= 0 && gate_per_head) {
+            const float gate = 1.0f / (1.0f + expf(-__bfloat162float(row[gate_offset + h])));
+            a *= gate;
+            b *= gate;
+          } else if (gate_offset >= 0) {
             const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(row + gate_offset + h * kVD + d);
             a *= 1.0f / (1.0f + expf(-__bfloat162float(gv.x)));
             b *= 1.0f / (1.0f + expf(-__bfloat162float(gv.y)));
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__(kThreads)
 
 // The parts of a row put together (see merge_mixed_kernel of the general kernel): a CTA per (row, head), a thread per output.
 __global__ void merge_mixed_decode_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ rows, int row_stride, int gate_offset,
-                                          __nv_bfloat16* __restrict__ out, int heads, int splits) {
+                                          __nv_bfloat16* __restrict__ out, int heads, int splits, int gate_per_head) {
   __shared__ float weight_s[64];   // at most 64 parts: each part's e^(max - highest)
   __shared__ float scratch[2];
   const int t = blockIdx.x, h = blockIdx.y;
@@ -312,7 +319,7 @@ __global__ void merge_mixed_decode_kernel(const float* __restrict__ partial, con
     }
     for (; s < splits; ++s) value[0] += mine[s * part_size + o] * weight_s[s];
     float v = ((value[0] + value[1]) + (value[2] + value[3])) * inv;
-    if (gate_offset >= 0) v *= 1.0f / (1.0f + expf(-__bfloat162float(rows[(size_t)t * row_stride + gate_offset + o])));
+    if (gate_offset >= 0) v *= 1.0f / (1.0f + expf(-__bfloat162float(rows[(size_t)t * row_stride + gate_offset + (gate_per_head ? h : o)])));
     out[(size_t)t * outputs + o] = __float2bfloat16_rn(v);
   }
 }
@@ -327,9 +334,10 @@ TLIE_EXPORT long long tlie_mixed_decode_smem_bytes(int heads, int mixed) { retur
 TLIE_EXPORT int tlie_mixed_decode(const void* rows, int row_stride, int gate_offset, const void* k_pages, long long k_page_stride, const void* v_pages,
                                   long long v_page_stride, const int* positions, const int* token_seq, const int* block_table, int table_stride,
                                   const float* slopes, const float* mix, void* out, int tokens, int heads, int page_size, int window, float scale, int splits,
-                                  float* partial, cudaStream_t stream) {
+                                  float* partial, int keep_first, int gate_per_head, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads <= 0 || heads % kG != 0 || heads / kG > 16 || row_stride % 8 != 0 || (gate_offset >= 0 && gate_offset % 2 != 0) || splits < 1 || splits > 64 ||
+  if (keep_first < 0) return (int)cudaErrorInvalidValue;
+  if (heads <= 0 || heads % kG != 0 || heads / kG > 16 || row_stride % 8 != 0 || (gate_offset >= 0 && !gate_per_head && gate_offset % 2 != 0) || splits < 1 || splits > 64 ||
       (splits > 1 && partial == nullptr))
     return (int)cudaErrorInvalidValue;
   const size_t smem = DecodeSmem(heads, mix != nullptr).total;
@@ -341,9 +349,9 @@ TLIE_EXPORT int tlie_mixed_decode(const void* rows, int row_stride, int gate_off
   mixed_decode_kernel<<<dim3(tokens, splits), kThreads, smem, stream>>>((const __nv_bfloat16*)rows, row_stride, gate_offset, (const __nv_bfloat16*)k_pages,
                                                                        k_page_stride, (const __nv_bfloat16*)v_pages, v_page_stride, positions, token_seq,
                                                                        block_table, table_stride, slopes, mix, (__nv_bfloat16*)out, heads, page_size, window,
-                                                                       scale, partial);
+                                                                       scale, partial, window > 0 ? keep_first : 0, gate_per_head);
   if (splits > 1)
     merge_mixed_decode_kernel<<<dim3(tokens, heads), kVD >= 128 ? 128 : (kVD > 32 ? 64 : 32), 0, stream>>>(partial, (const __nv_bfloat16*)rows, row_stride,
-                                                                                                        gate_offset, (__nv_bfloat16*)out, heads, splits);
+                                                                                                        gate_offset, (__nv_bfloat16*)out, heads, splits, gate_per_head);
   return (int)cudaGetLastError();
 }

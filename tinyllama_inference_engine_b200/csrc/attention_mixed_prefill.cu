@@ -100,12 +100,12 @@ struct TileRows {
   int slot[kKeys / 16];
 };
 
-__device__ __forceinline__ TileRows tile_rows(const int* table, int key0, int lo, int n_keys, int page_size) {
+__device__ __forceinline__ TileRows tile_rows(const int* table, int key0, int lo, int n_keys, int page_size, int keep) {
   TileRows rows;
 #pragma unroll
   for (int h = 0; h < kKeys / 16; ++h) {
     const int k = key0 + 16 * h;
-    const bool any = k < n_keys && k + 16 > lo;
+    const bool any = k < n_keys && (k + 16 > lo || k < keep);
     rows.page[h] = any ? table[k / page_size] : 0;
     rows.slot[h] = k % page_size;
   }
@@ -115,12 +115,12 @@ __device__ __forceinline__ TileRows tile_rows(const int* table, int key0, int lo
 // one plane's rows of a tile for one head: [64][row] in shared memory, ``width`` elements each
 template <int WIDTH, int ROW>
 __device__ __forceinline__ void load_plane(__nv_bfloat16* smem, const __nv_bfloat16* pages, long long page_stride, const TileRows& rows, int key0, int lo,
-                                           int n_keys, int head, int page_size) {
+                                           int n_keys, int head, int page_size, int keep) {
   constexpr int kChunks = WIDTH / 8;
   for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kThreads) {
     const int chunk = idx % kChunks, row = idx / kChunks;
     const int key = key0 + row, quarter = row >> 4;
-    const bool valid = key >= lo && key < n_keys;
+    const bool valid = (key >= lo || key < keep) && key < n_keys;
     const long long page = quarter == 0 ? rows.page[0] : quarter == 1 ? rows.page[1] : quarter == 2 ? rows.page[2] : rows.page[3];
     const int slot = (quarter == 0 ? rows.slot[0] : quarter == 1 ? rows.slot[1] : quarter == 2 ? rows.slot[2] : rows.slot[3]) + (row & 15);
     const __nv_bfloat16* src = pages + page * page_stride + ((size_t)head * page_size + slot) * WIDTH + chunk * 8;
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
                          const __nv_bfloat16* __restrict__ k_pages, long long k_page_stride, const __nv_bfloat16* __restrict__ v_pages,
                          long long v_page_stride, const int* __restrict__ seq_starts, const int* __restrict__ first_positions,
                          const int* __restrict__ block_table, int table_stride, const float* __restrict__ slopes, __nv_bfloat16* __restrict__ out,
-                         int heads, int kv_heads, int page_size, int window, int mixed) {
+                         int heads, int kv_heads, int page_size, int window, int mixed, int keep_first, int gate_per_head) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kRows][kQRow]
   __nv_bfloat16* k_ring = q_smem + (size_t)kRows * kQRow;                        // [kRing][kPartsPerChunk][64][kKRow]
@@ -168,18 +168,23 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
 
   const int first_tile = lo_tile / kKeys;
   const int end_tile = (n_keys + kKeys - 1) / kKeys;
-  const int chunks = (end_tile - first_tile) * kChunksPerTile;   // chunk c: key heads [c % per tile * kPartsPerChunk, ...) of tile first_tile + c / per tile
+  // With a window, the keys below ``keep`` stay visible behind it: the tiles that hold them and lie before the window's first tile
+  // come first (those from the window's first tile on are loaded anyway; a key is masked per row).
+  const int keep = window > 0 ? keep_first : 0;
+  const int kept_tiles = min((keep + kKeys - 1) / kKeys, first_tile);
+  const int chunks = (kept_tiles + end_tile - first_tile) * kChunksPerTile;   // chunk c: key heads [c % per tile * kPartsPerChunk, ...) of the (c / per tile)-th tile
+  auto tile_of = [&](int c) { const int n = c / kChunksPerTile; return n < kept_tiles ? n : first_tile + (n - kept_tiles); };
   auto issue = [&](int c) {
     if (c < chunks) {
-      const int tile = first_tile + c / kChunksPerTile, first_part = (c % kChunksPerTile) * kPartsPerChunk;
-      const TileRows rows_of = tile_rows(table, tile * kKeys, lo_tile, n_keys, page_size);
+      const int tile = tile_of(c), first_part = (c % kChunksPerTile) * kPartsPerChunk;
+      const TileRows rows_of = tile_rows(table, tile * kKeys, lo_tile, n_keys, page_size, keep);
 #pragma unroll
       for (int i = 0; i < kPartsPerChunk; ++i)
         load_plane<kD, kKRow>(k_ring + (size_t)(c % kRing) * kChunkElements + (size_t)i * kKeys * kKRow, k_pages, k_page_stride, rows_of, tile * kKeys, lo_tile, n_keys,
-                              mixed ? first_part + i : kvh, page_size);
+                              mixed ? first_part + i : kvh, page_size, keep);
       if (first_part == 0)
         load_plane<kVD, kVRow>(v_ring + (size_t)((c / kChunksPerTile) % kVBuffers) * kKeys * kVRow, v_pages, v_page_stride, rows_of, tile * kKeys, lo_tile, n_keys, kvh,
-                               page_size);
+                               page_size, keep);
     }
     cp_async_commit();   // a group per chunk, empty past the end, so that the count of groups in flight is the same at every step
   };
@@ -204,14 +209,15 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
     issue(c + kRing - 1);
     cp_async_wait<kRing - 1>();   // everything but the chunks issued ahead has landed: chunk c, and its tile's values
     __syncthreads();
-    const int tile = first_tile + c / kChunksPerTile, first_part = (c % kChunksPerTile) * kPartsPerChunk;
+    const int tile = tile_of(c), first_part = (c % kChunksPerTile) * kPartsPerChunk;
     const __nv_bfloat16* k_smem = k_ring + (size_t)(c % kRing) * kChunkElements;
     const __nv_bfloat16* v_smem = v_ring + (size_t)((c / kChunksPerTile) % kVBuffers) * kKeys * kVRow;
     const int key0 = tile * kKeys;
     const int warp_last_pos = pos0 + min(warp * 16 + 15, rows_here - 1);
     const int warp_first_pos = pos0 + min(warp * 16, rows_here - 1);
     const int warp_lo = (window > 0 && warp_first_pos - window + 1 > 0) ? warp_first_pos - window + 1 : 0;
-    if (key0 <= warp_last_pos && key0 + kKeys > warp_lo) {   // some row of this warp sees some key of this tile
+    const bool tile_seen = key0 <= warp_last_pos && (key0 + kKeys > warp_lo || key0 < keep);   // some row of this warp sees some key of this tile
+    if (tile_seen) {
       if (first_part == 0) {
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) s_frag[j][0] = s_frag[j][1] = s_frag[j][2] = s_frag[j][3] = 0.0f;
@@ -234,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
         }
       }
     }
-    if (first_part + kPartsPerChunk == kParts && key0 <= warp_last_pos && key0 + kKeys > warp_lo) {
+    if (first_part + kPartsPerChunk == kParts && tile_seen) {
       // scores in units of log2: (dot - slope (i - j)) log2 e; keys outside a row's window or after it are masked
       float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -243,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + j * 8 + 2 * t + (e & 1);
           const int r = e >> 1;
-          const float v = (key >= my_lo[r] && key <= my_pos[r]) ? fmaf(s_frag[j][e], kLog2e, -slope * (float)(my_pos[r] - key)) : -INFINITY;
+          const float v = ((key >= my_lo[r] || key < keep) && key <= my_pos[r]) ? fmaf(s_frag[j][e], kLog2e, -slope * (float)(my_pos[r] - key)) : -INFINITY;
           s_frag[j][e] = v;
           tile_max[r] = fmaxf(tile_max[r], v);
         }
@@ -305,10 +311,11 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
     const float inv = 1.0f / row_sum[r];
     const size_t row = (size_t)(row0 + my_row[r]);
     __nv_bfloat16* dst = out + (row * heads + head) * kVD + 2 * t;
-    const __nv_bfloat16* gate = gate_offset >= 0 ? rows + row * row_stride + gate_offset + (size_t)head * kVD + 2 * t : nullptr;
+    const __nv_bfloat16* gate = (gate_offset >= 0 && !gate_per_head) ? rows + row * row_stride + gate_offset + (size_t)head * kVD + 2 * t : nullptr;
+    const float head_gate = (gate_offset >= 0 && gate_per_head) ? 1.0f / (1.0f + __expf(-__bfloat162float(rows[row * row_stride + gate_offset + head]))) : 1.0f;
 #pragma unroll
     for (int i = 0; i < kVD / 8; ++i) {
-      float a = o[i][r * 2] * inv, b = o[i][r * 2 + 1] * inv;
+      float a = o[i][r * 2] * inv * head_gate, b = o[i][r * 2 + 1] * inv * head_gate;
       if (gate != nullptr) {
         const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(gate + i * 8);
         a *= 1.0f / (1.0f + __expf(-__bfloat162float(gv.x)));
@@ -331,10 +338,12 @@ TLIE_EXPORT int tlie_mixed_prefill_folded_width() { return kParts * kD; }
 TLIE_EXPORT int tlie_mixed_prefill(const void* rows, int row_stride, int gate_offset, const float* mix, float scale, void* folded, const void* k_pages,
                                    long long k_page_stride, const void* v_pages, long long v_page_stride, const int* seq_starts,
                                    const int* first_positions, const int* block_table, int table_stride, const float* slopes, void* out, int tokens,
-                                   int entries, int longest, int heads, int kv_heads, int page_size, int window, cudaStream_t stream) {
+                                   int entries, int longest, int heads, int kv_heads, int page_size, int window, int keep_first, int gate_per_head,
+                                   cudaStream_t stream) {
   if (tokens <= 0 || entries <= 0) return 0;
+  if (keep_first < 0) return (int)cudaErrorInvalidValue;
   if (kRows == 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size % 16 != 0 || heads > 65535 || entries > 65535 ||
-      (mix != nullptr ? kParts != kv_heads : kParts != 1) || row_stride % 8 != 0 || (gate_offset >= 0 && gate_offset % 2 != 0))
+      (mix != nullptr ? kParts != kv_heads : kParts != 1) || row_stride % 8 != 0 || (gate_offset >= 0 && !gate_per_head && gate_offset % 2 != 0))
     return (int)cudaErrorInvalidValue;
   const size_t fold_smem = ((size_t)heads * kD + (mix != nullptr ? (size_t)heads * heads : 0)) * sizeof(float);
   if (fold_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -358,6 +367,6 @@ TLIE_EXPORT int tlie_mixed_prefill(const void* rows, int row_stride, int gate_of
   mixed_prefill_kernel<<<grid, kThreads, smem, stream>>>((const __nv_bfloat16*)folded, (const __nv_bfloat16*)rows, row_stride, gate_offset,
                                                          (const __nv_bfloat16*)k_pages, k_page_stride, (const __nv_bfloat16*)v_pages, v_page_stride,
                                                          seq_starts, first_positions, block_table, table_stride, slopes, (__nv_bfloat16*)out, heads,
-                                                         kv_heads, page_size, window, mix != nullptr ? 1 : 0);
+                                                         kv_heads, page_size, window, mix != nullptr ? 1 : 0, keep_first, gate_per_head);
   return (int)cudaGetLastError();
 }

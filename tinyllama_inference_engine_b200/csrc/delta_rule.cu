@@ -90,7 +90,7 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ rows, int row_stri
   for (int i = 0; i < taps - 1; ++i) conv_state[(size_t)i * channels + c] = keep[i];
 }
 
-// R: key channels per lane (dim <= 8 R).
+// R: key channels a lane has registers for (dim <= 8 R); the state holds ceil(dim / 8) of them per lane.
 template <int R>
 __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
@@ -108,7 +108,8 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   const int kv = head / (heads / kv_heads);
   const int qk = kv_heads * dim;
   const int width = 2 * qk + heads * vdim + heads + heads * dim;
-  const size_t matrix = (size_t)R * vdim * kDeltaLanes;
+  const int held = (dim + kDeltaLanes - 1) / kDeltaLanes;   // key channels per lane that exist (and are stored)
+  const size_t matrix = (size_t)held * vdim * kDeltaLanes;
   float* mine = state + (size_t)state_slots[entry] * state_stride + (size_t)head * matrix;
 
   // where each word of a staged row comes from in a prep row (-1: padding, reads as zero)
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   }
   float S[R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = live ? mine[((size_t)i * vdim + column) * kDeltaLanes + lane] : 0.0f;
+  for (int i = 0; i < R; ++i) S[i] = (live && i < held) ? mine[((size_t)i * vdim + column) * kDeltaLanes + lane] : 0.0f;
 
   float fetched[kLoads];
   auto fetch = [&](int row) {
@@ -175,7 +176,8 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   }
   if (live && count > 0) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) mine[((size_t)i * vdim + column) * kDeltaLanes + lane] = S[i];
+    for (int i = 0; i < R; ++i)
+      if (i < held) mine[((size_t)i * vdim + column) * kDeltaLanes + lane] = S[i];
   }
 }
 

@@ -655,20 +655,21 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     if pages.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: pages and rows differ in dtype", code="invalid_dtype")
     table = cache.block_table
-    plain_options = keep_first == 0 and not gate_per_head and sinks is None and not values_in_keys   # what the tensor-core kernels know
-    if plain_options and rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset):
+    plain_options = sinks is None and not values_in_keys   # what the tensor-core kernels know
+    if plain_options and rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset,
+                                                                                   gate_per_head):
         folded = folded_slopes if folded_slopes is not None else fast.folded_slopes(slopes, mix)
         fast.mixed_prefill(rows, gate_offset, batch, table, (k_ptr, k_stride, v_ptr, v_stride), folded, mix, out, heads, kv_heads, key_dim, value_dim,
-                           cache.page_size, window, scale)
+                           cache.page_size, window, scale, keep_first if window > 0 else 0, gate_per_head)
         return
     # few rows over long contexts (decode steps): every row's keys are dealt to several CTAs
     splits, partial = 1, None
     if batch is not None and tokens * 2 <= fast.sm_count():
         reach = min(window + keep_first, batch.max_seq_len) if window > 0 else batch.max_seq_len
         splits = max(1, min(2 * fast.sm_count() // tokens, -(-reach // 32), 64))   # down to one tile of 32 keys per CTA
-        if plain_options and fast.mixed_decode_takes(rows, heads, kv_heads, key_dim, value_dim, gate_offset, mix is not None):
+        if plain_options and fast.mixed_decode_takes(rows, heads, kv_heads, key_dim, value_dim, gate_offset, mix is not None, gate_per_head):
             fast.mixed_decode(rows, gate_offset, positions, token_seq, table, (k_ptr, k_stride, v_ptr, v_stride), slopes, mix, out, heads, kv_heads, key_dim,
-                              value_dim, cache.page_size, window, scale, splits)
+                              value_dim, cache.page_size, window, scale, splits, keep_first if window > 0 else 0, gate_per_head)
             return
         if splits > 1:
             partial = fast.mixed_scratch(rows.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32)

@@ -693,12 +693,12 @@ def mixed_prefill_library(key_dim: int, value_dim: int, parts: int):
     return lib
 
 
-def mixed_prefill_takes(batch, rows, page_size: int, parts: int, key_dim: int, value_dim: int, gate_offset: int) -> bool:
+def mixed_prefill_takes(batch, rows, page_size: int, parts: int, key_dim: int, value_dim: int, gate_offset: int, gate_per_head: bool = False) -> bool:
     """Whether a step's attention with mixed heads runs on the tensor-core kernel: bfloat16, a prompt portion among the entries,
     widths that are multiples of 16, and tiles that fit shared memory (the kernel set says how many rows its tile has: 0 = none)."""
     if not use_mixed_prefill or batch is None or batch.max_q_len < MIXED_PREFILL_MIN_ROWS or rows.dtype != torch.bfloat16:
         return False
-    if key_dim % 16 or value_dim % 16 or page_size % 16 or rows.shape[1] % 8 or (gate_offset >= 0 and gate_offset % 2) or batch.num_seqs > 65535:
+    if key_dim % 16 or value_dim % 16 or page_size % 16 or rows.shape[1] % 8 or (gate_offset >= 0 and not gate_per_head and gate_offset % 2) or batch.num_seqs > 65535:
         return False
     if ((parts * key_dim + 8) * 16 + 3 * 64 * (key_dim + 8) + (3 if parts == 1 else 2) * 64 * (value_dim + 8)) * 2 > 227 * 1024:
         return False   # not even 16 rows of folded queries fit beside the rings of keys and values
@@ -727,10 +727,11 @@ def mixed_scratch(device: torch.device, elements: int, dtype: torch.dtype) -> to
 
 
 def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
-                  page_size: int, window: int, scale: float) -> None:
+                  page_size: int, window: int, scale: float, keep_first: int = 0, gate_per_head: bool = False) -> None:
     """Attention with mixed heads for a step that carries prompt portions (csrc/attention_mixed_prefill.cu): the mix is folded into
     the queries by a first kernel, the second is flash attention over the concatenated key heads.  ``planes``: (key plane pointer,
-    its page stride in elements, value plane pointer, its page stride); ``folded``: the folded slopes (``folded_slopes``) or None."""
+    its page stride in elements, value plane pointer, its page stride); ``folded``: the folded slopes (``folded_slopes``) or None.
+    ``keep_first``: with a window, the keys below this position stay visible; ``gate_per_head``: the gate is one column per head."""
     ops = _ops()
     parts = kv_heads if mix is not None else 1
     tokens = rows.shape[0]
@@ -742,7 +743,7 @@ def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mi
             ops._ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), ops._ptr(mix), c_float(scale), ops._ptr(held), k_ptr, c_longlong(k_stride), v_ptr,
             c_longlong(v_stride), ops._i32(batch.seq_starts, "seq_starts"), ops._i32(batch.first_positions, "first_positions"), ops._i32(block_table, "block_table"),
             c_int(block_table.shape[1]), ops._ptr(folded), ops._ptr(out), c_int(tokens), c_int(batch.num_seqs), c_int(batch.max_q_len),
-            c_int(heads), c_int(kv_heads), c_int(page_size), c_int(window), ops._stream()),
+            c_int(heads), c_int(kv_heads), c_int(page_size), c_int(window), c_int(keep_first), c_int(1 if gate_per_head else 0), ops._stream()),
         "mixed_prefill")
     ops.launch_count += 1   # two kernels: the fold and the attention
 
@@ -761,19 +762,19 @@ def mixed_decode_library(key_dim: int, value_dim: int, kv_heads: int):
     return lib
 
 
-def mixed_decode_takes(rows, heads: int, kv_heads: int, key_dim: int, value_dim: int, gate_offset: int, mixed: bool) -> bool:
+def mixed_decode_takes(rows, heads: int, kv_heads: int, key_dim: int, value_dim: int, gate_offset: int, mixed: bool, gate_per_head: bool = False) -> bool:
     """Whether a step of few rows runs its attention with mixed heads on the tensor-core decode kernel: bfloat16, widths that are
     multiples of 16, at most 16 heads per key/value head, and a tile that fits shared memory."""
     if not use_mixed_decode or rows.dtype != torch.bfloat16 or key_dim % 16 or value_dim % 16 or heads // kv_heads > 16 or rows.shape[1] % 8:
         return False
-    if gate_offset >= 0 and gate_offset % 2:
+    if gate_offset >= 0 and not gate_per_head and gate_offset % 2:
         return False
     fixed = 512 + kv_heads * (16 * (key_dim + 8) + 32 * (key_dim + 8) + 32 * (value_dim + 8) + 16 * 40) * 2
     return fixed + heads * 32 * 4 + (heads * heads * 4 if mixed else 0) + 3 * heads * 4 + 16 <= 200 * 1024
 
 
 def mixed_decode(rows, gate_offset: int, positions, token_seq, block_table, planes, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
-                 page_size: int, window: int, scale: float, splits: int) -> None:
+                 page_size: int, window: int, scale: float, splits: int, keep_first: int = 0, gate_per_head: bool = False) -> None:
     """Attention with mixed heads for a step of few rows (csrc/attention_mixed_decode.cu).  ``planes`` as in ``mixed_prefill``;
     ``splits``: CTAs that share a row's key tiles (their parts are merged by a second kernel)."""
     ops = _ops()
@@ -784,7 +785,8 @@ def mixed_decode(rows, gate_offset: int, positions, token_seq, block_table, plan
         mixed_decode_library(key_dim, value_dim, kv_heads).tlie_mixed_decode(
             ops._ptr(rows), c_int(rows.shape[1]), c_int(gate_offset), k_ptr, c_longlong(k_stride), v_ptr, c_longlong(v_stride), ops._i32(positions, "positions"),
             ops._i32(token_seq, "token_seq"), ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(slopes), ops._ptr(mix), ops._ptr(out),
-            c_int(tokens), c_int(heads), c_int(page_size), c_int(window), c_float(scale), c_int(splits), ops._ptr(partial), ops._stream()),
+            c_int(tokens), c_int(heads), c_int(page_size), c_int(window), c_float(scale), c_int(splits), ops._ptr(partial), c_int(keep_first),
+            c_int(1 if gate_per_head else 0), ops._stream()),
         "mixed_decode")
 
 

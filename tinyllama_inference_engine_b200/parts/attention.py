@@ -239,6 +239,9 @@ class NormedKeyAttention(Mixer):
         if spec.get("head_gate"):
             self.gate_offset = width
             stacked.append(weights.get(f"{prefix}.g", dtype))
+            width += self.heads
+        if width % 8:   # rows of the stacked product start on 16-byte boundaries (what the tensor-core attention kernels read them by)
+            stacked.append(torch.zeros((8 - width % 8, self.hidden), dtype=dtype, device=stacked[0].device))
         self.w_in = torch.cat(stacked, dim=0).contiguous()
         self.w_o = weights.get(f"{prefix}.o", dtype).contiguous()
 
