@@ -370,6 +370,36 @@ def design_configs(size: dict) -> tuple[dict, dict]:
     return marutar, llama
 
 
+# `--designs zirutar`: Zirutar (the gated delta rule, attention with normalised keys under a window that keeps the first tokens, latent
+# attention with a sink; clamped gated feed-forwards; a gated slice of a second token table per layer) beside Marutar, the closest of
+# the engine's designs (a recurrence per request and windowed, gated attention over pages), at equal width, feed-forward width, layer
+# count, vocabulary and attention heads.
+ZIRUTAR_SIZES = {
+    "w2048": dict(delta_heads=16, delta_dim=128, delta_vdim=128, taps=4, low_rank=64, latent_heads=16, plain=128, rot=64, latent_vdim=128, rank=512, keep=4, side=256,
+                  limit=7.0, pattern=("channel_delta", "channel_delta", "attention", "latent_attention")),
+    "w4096": dict(delta_heads=32, delta_dim=128, delta_vdim=128, taps=4, low_rank=128, latent_heads=16, plain=128, rot=64, latent_vdim=128, rank=512, keep=4, side=256,
+                  limit=7.0, pattern=("channel_delta", "attention", "latent_attention", "attention")),
+}
+
+
+def zirutar_config(size: dict, extra: dict) -> dict:
+    layers = []
+    for index in range(size["layers"]):
+        kind = extra["pattern"][index % len(extra["pattern"])]
+        if kind == "channel_delta":
+            mixer = {"heads": extra["delta_heads"], "kv_heads": extra["delta_heads"], "dim": extra["delta_dim"], "vdim": extra["delta_vdim"], "conv": extra["taps"],
+                     "decay_rank": extra["low_rank"], "gate_rank": extra["low_rank"]}
+        elif kind == "attention":
+            mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
+                     "mask": {"size": size["window"], "keep_first": extra["keep"]}}
+        else:
+            mixer = {"heads": extra["latent_heads"], "dim": extra["plain"], "rot_dim": extra["rot"], "vdim": extra["latent_vdim"], "kv_rank": extra["rank"],
+                     "scale": (extra["plain"] + extra["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": extra["rot"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"], "limit": extra["limit"]}})
+    return {"architecture": "Zirutar", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": size["width"] ** 0.5},
+            "logit_scale": 1.0, "token_side": {"dim": extra["side"]}, "layers": layers}
+
+
 def run_designs(args) -> dict:
     import numpy as np
     import torch
@@ -501,19 +531,103 @@ def run_designs(args) -> dict:
             out[f"mingru_scan_{name}"] = {"ms": scan_ms, "gbs": moved / scan_ms / 1e6, "frac": moved / (scan_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
         return out
 
+    def zirutar_kernel_numbers(size: dict, extra: dict) -> dict:
+        """Zirutar's own kernels alone against their rooflines, beside Marutar's like kernels (its attention at the same heads, widths and
+        window; its scan over as many channels as the delta rule has value channels)."""
+        H, G, D, W = size["heads"], size["kv_heads"], size["dim"], size["window"]
+        DH, DD, DV = extra["delta_heads"], extra["delta_dim"], extra["delta_vdim"]
+        LH, rank, rot = extra["latent_heads"], extra["rank"], extra["rot"]
+        page, bf16 = 64, torch.bfloat16
+        out = {}
+        pages_needed = -(-(context + 1) // page) * batch + -(-prompt_tokens // page)
+        pages = torch.randn(pages_needed, 2, G, page, D, dtype=torch.float32, device=device).to(bf16)
+        latent_pages = torch.randn(pages_needed, 1, 1, page, rank + rot, dtype=torch.float32, device=device).to(bf16)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32, device=device)
+        mix = (torch.randn(H, H, device=device) * H ** -0.5).contiguous()
+        folded = fast.folded_slopes(slopes, mix)
+        sinks = torch.zeros(LH, device=device)
+
+        def context_for(lens, firsts):
+            table_width = size["positions"] // page
+            rows, at = [], 0
+            for n, f in zip(lens, firsts):
+                count = -(-(f + n) // page)
+                rows.append(list(range(at, at + count)) + [-1] * (table_width - count))
+                at += count
+            entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lens)]
+            return pack_step(entries, list(firsts), list(range(len(lens))), [rows], device)
+
+        for name, lens, firsts in (("prefill", [prompt_tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            ctx = context_for(lens, firsts)
+            tokens = sum(lens)
+            cache = LayerCache(CacheNeed("pages"), True, pages, ctx.block_tables[0], page)
+            latent_cache = LayerCache(CacheNeed("pages"), True, latent_pages, ctx.block_tables[0], page)
+            windowed = sum(min(f + i + 1, W) for n, f in zip(lens, firsts) for i in range(n))
+            causal = sum(f + i + 1 for n, f in zip(lens, firsts) for i in range(n))
+            width = -(-(H * D + G * D + H) // 8) * 8
+            rows = torch.randn(tokens, width, device=device).to(bf16)
+            mixed = torch.empty(tokens, H * D, dtype=bf16, device=device)
+            ms = timed(lambda: ops.mixed_heads_attention(rows, H * D + G * D, ctx.positions, ctx.token_seq, cache, None, None, mixed, H, G, D, D, W, D ** -0.5, batch=ctx,
+                                                         keep_first=extra["keep"], gate_per_head=True))
+            like_rows = torch.randn(tokens, H * D + 2 * G * D + H * D, device=device).to(bf16)
+            like_ms = timed(lambda: ops.mixed_heads_attention(like_rows, H * D + 2 * G * D, ctx.positions, ctx.token_seq, cache, slopes, mix, mixed, H, G, D, D, W, D ** -0.5,
+                                                              batch=ctx, folded_slopes=folded))
+            queries = torch.randn(tokens, LH * (rank + rot), device=device).to(bf16)
+            summed = torch.empty(tokens, LH * rank, dtype=bf16, device=device)
+            latent_ms = timed(lambda: ops.mixed_heads_attention(queries, -1, ctx.positions, ctx.token_seq, latent_cache, None, None, summed, LH, 1, rank + rot, rank, 0,
+                                                                (extra["plain"] + rot) ** -0.5, batch=ctx, sinks=sinks, values_in_keys=True))
+            if name == "prefill":
+                flops, like_flops = windowed * H * 4.0 * D, windowed * H * (4.0 * D + 2.0 * H)
+                latent_flops = causal * LH * 2.0 * (2 * rank + rot)
+                out["attention_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+                                            "like_ms": like_ms, "like_tflops": like_flops / like_ms / 1e9, "like_frac": like_flops / (like_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+                out["latent_attention_prefill"] = {"ms": latent_ms, "tflops": latent_flops / latent_ms / 1e9, "frac": latent_flops / (latent_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+            else:
+                moved = windowed * G * 2 * D * 2.0
+                latent_moved = causal * (rank + rot) * 2.0
+                out["attention_decode"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                           "like_ms": like_ms, "like_gbs": moved / like_ms / 1e6, "like_frac": moved / (like_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+                out["latent_attention_decode"] = {"ms": latent_ms, "gbs": latent_moved / latent_ms / 1e6, "frac": latent_moved / (latent_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            # the delta rule's recurrence, and Marutar's scan over as many channels as the rule has value channels
+            channels = 2 * DH * DD + DH * DV
+            prep = torch.rand(tokens, channels + DH + DH * DD, device=device)
+            words, _ = ops.delta_state_words(DH, DD, DV, channels, extra["taps"])
+            state = torch.zeros(batch + 1, words, device=device)
+            read = torch.empty(tokens, DH * DV, device=device)
+            rule_ms = timed(lambda: ops.delta_rule(prep, state, ctx, read, DH, DH, DD, DV))
+            rule_flops = tokens * DH * DD * DV * 7.0
+            rule_moved = tokens * 4.0 * (prep.shape[1] + DH * DV) + len(lens) * DH * DD * DV * 8.0
+            R = DH * DV
+            zxg = torch.randn(tokens, 3 * R, device=device).to(bf16)
+            gated = torch.empty(tokens, R, dtype=bf16, device=device)
+            scan_state = torch.zeros(batch + 1, R, device=device)
+            bias = torch.zeros(R, device=device)
+            scan_ms = timed(lambda: ops.mingru_scan(zxg, bias, bias, scan_state, ctx.seq_starts, ctx.state_slots, gated, max(lens)))
+            scan_moved = tokens * 4.0 * R * 2 + (len(lens) * R * 8 if name == "decode" else 0)
+            out[f"delta_rule_{name}"] = {"ms": rule_ms, "gbs": rule_moved / rule_ms / 1e6, "frac": rule_moved / (rule_ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                         "fp32_tflops": rule_flops / rule_ms / 1e9, "like_ms": scan_ms, "like_gbs": scan_moved / scan_ms / 1e6,
+                                         "like_frac": scan_moved / (scan_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+        return out
+
     results = {}
+    which = args.designs
     with ClockSampler() as clocks:
         for key, size in DESIGN_SIZES.items():
             marutar, llama = design_configs(size)
             base = Path(tempfile.gettempdir()) / f"tlie_b200_designs_{os.getuid()}_{key}"
+            pair = (("marutar", marutar), ("llama", llama)) if which == "marutar" else (("zirutar", zirutar_config(size, ZIRUTAR_SIZES[key])), ("marutar", marutar))
             folders = {}
-            for name, config in (("marutar", marutar), ("llama", llama)):
+            for name, config in pair:
                 folders[name] = base / name
                 if not (folders[name] / "model.safetensors").exists():
                     write_random_model(folders[name], config, seed=0)
-            results[key] = {"marutar": model_numbers(folders["marutar"]), "llama": model_numbers(folders["llama"]), "kernels": kernel_numbers(size),
-                            "sizes": {k: v for k, v in size.items() if k != "pattern"} | {"pattern": "/".join(size["pattern"])}}
-    return {"metric": "prompt and decode throughput of Marutar beside the Llama decoder at equal sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            results[key] = {name: model_numbers(folders[name]) for name, _ in pair}
+            results[key]["kernels"] = kernel_numbers(size) if which == "marutar" else zirutar_kernel_numbers(size, ZIRUTAR_SIZES[key])
+            results[key]["sizes"] = {k: v for k, v in size.items() if k != "pattern"} | {"pattern": "/".join(size["pattern"])}
+            if which == "zirutar":
+                results[key]["sizes"] |= {k: v for k, v in ZIRUTAR_SIZES[key].items() if k != "pattern"} | {"zirutar_pattern": "/".join(ZIRUTAR_SIZES[key]["pattern"])}
+    names = "Marutar beside the Llama decoder" if which == "marutar" else "Zirutar beside Marutar"
+    return {"metric": f"prompt and decode throughput of {names} at equal sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)", "impl": "engine", "higher_is_better": True,
             "config": {"prompt_tokens": prompt_tokens, "decode_context": context, "decode_batch": batch, "decode_steps": steps, "page_size": 64, "peaks": peak_kind,
                        "l2": "a buffer larger than L2 is written before every timed launch"},
@@ -573,8 +687,9 @@ def main() -> int:
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
     parser.add_argument("--sections", default="decode,e2e,prefill,points,mixed", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
-    parser.add_argument("--designs", action="store_true", help="instead of the headline workload: Marutar beside the Llama decoder at equal sizes (prompt and decode "
-                                                               "throughput through the engine, and the design's own kernels against their rooflines)")
+    parser.add_argument("--designs", nargs="?", const="marutar", default=None, choices=["marutar", "zirutar"],
+                        help="instead of the headline workload: another design beside the closest existing one at equal sizes (prompt and decode throughput through "
+                             "the engine, and the design's own kernels against their rooflines): Marutar beside the Llama decoder (the default), or Zirutar beside Marutar")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")

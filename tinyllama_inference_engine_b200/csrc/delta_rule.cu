@@ -12,8 +12,8 @@
 //                    from the request's convolution state) with silu, unit norms of q and k per head, q's scale,
 //                    beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)): all 32-bit, into one row of ``prep``
 //   delta_conv_state per entry: the last taps - 1 inputs of the convolution, kept for the next step
-//   delta_rule       the recurrence: one CTA per (entry, head, 16 columns), rows in order, the next row's operands fetched
-//                    while the current one is worked on
+//   delta_rule       the recurrence: one CTA per (entry, head, 16 columns), rows in order, the operands of the next seven rows
+//                    on their way (asynchronous copies into a ring) while the current one is worked on
 //   delta_gate_norm  per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
 //
 // State of a request (32-bit words): for every head the matrix in the order the recurrence reads it,
@@ -90,12 +90,24 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ rows, int row_stri
   for (int i = 0; i < taps - 1; ++i) conv_state[(size_t)i * channels + c] = keep[i];
 }
 
+constexpr int kDeltaStages = 8;   // rows whose operands are in flight or staged ahead of the one being worked on
+
+__device__ __forceinline__ void delta_copy_word(float* dst, const float* src) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(to), "l"(src));
+}
+__device__ __forceinline__ void delta_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void delta_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // R: key channels a lane has registers for (dim <= 8 R); the state holds ceil(dim / 8) of them per lane.
+// A row's operands ([q | k | g] of the head, the CTA's 16 values, beta) are copied asynchronously into a ring of kDeltaStages
+// buffers, several rows ahead, so that a row's turn never waits for memory; padding words are zeroed once and never copied.
 template <int R>
 __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
                                                                   int heads, int kv_heads, int dim, int vdim) {
-  extern __shared__ float stage_s[];   // two buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta]
+  extern __shared__ float stage_s[];   // kDeltaStages buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta]
   constexpr int kPadded = kDeltaLanes * R;
   constexpr int kRow = 3 * kPadded + kDeltaColumns + 1;
   constexpr int kLoads = (kRow + kDeltaThreads - 1) / kDeltaThreads;
@@ -112,7 +124,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   const size_t matrix = (size_t)held * vdim * kDeltaLanes;
   float* mine = state + (size_t)state_slots[entry] * state_stride + (size_t)head * matrix;
 
-  // where each word of a staged row comes from in a prep row (-1: padding, reads as zero)
+  // where each word of a staged row comes from in a prep row (-1: padding, stays zero)
   int source[kLoads];
 #pragma unroll
   for (int i = 0; i < kLoads; ++i) {
@@ -125,29 +137,29 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
     else if (w == 3 * kPadded + kDeltaColumns) at = 2 * qk + heads * vdim + head;
     source[i] = at;
   }
+  for (int i = tid; i < kDeltaStages * kRow; i += kDeltaThreads) stage_s[i] = 0.0f;
+  __syncthreads();
   float S[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) S[i] = (live && i < held) ? mine[((size_t)i * vdim + column) * kDeltaLanes + lane] : 0.0f;
 
-  float fetched[kLoads];
-  auto fetch = [&](int row) {
-    const float* from = prep + (size_t)(first + row) * width;
+  auto issue = [&](int row) {   // one group per row, empty past the end, so that the count of groups in flight is the same at every step
+    if (row < count) {
+      const float* from = prep + (size_t)(first + row) * width;
+      float* to = stage_s + (row % kDeltaStages) * kRow;
 #pragma unroll
-    for (int i = 0; i < kLoads; ++i) fetched[i] = source[i] >= 0 ? from[source[i]] : 0.0f;
+      for (int i = 0; i < kLoads; ++i)
+        if (source[i] >= 0) delta_copy_word(to + tid + i * kDeltaThreads, from + source[i]);
+    }
+    delta_commit();
   };
-  auto put = [&](int buffer) {
 #pragma unroll
-    for (int i = 0; i < kLoads; ++i)
-      if (tid + i * kDeltaThreads < kRow) stage_s[buffer * kRow + tid + i * kDeltaThreads] = fetched[i];
-  };
-  if (count > 0) {
-    fetch(0);
-    put(0);
-  }
-  __syncthreads();
+  for (int ahead = 0; ahead < kDeltaStages - 1; ++ahead) issue(ahead);
   for (int row = 0; row < count; ++row) {
-    const float* cur = stage_s + (row & 1) * kRow;
-    if (row + 1 < count) fetch(row + 1);
+    delta_wait<kDeltaStages - 2>();   // this thread's copies of this row have landed ...
+    __syncthreads();                  // ... and so have everyone's; and everyone is done with the row before, whose buffer is written next
+    issue(row + kDeltaStages - 1);
+    const float* cur = stage_s + (row % kDeltaStages) * kRow;
     float reach = 0.0f, read = 0.0f, both = 0.0f;   // k . (g S)_j, q . (g S)_j, q . k  (this lane's share)
     float kk[R];
 #pragma unroll
@@ -171,9 +183,8 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
     if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
-    if (row + 1 < count) put((row + 1) & 1);
-    __syncthreads();
   }
+  delta_wait<0>();
   if (live && count > 0) {
 #pragma unroll
     for (int i = 0; i < R; ++i)
@@ -199,7 +210,7 @@ template <int R>
 static int launch_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
                              int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
-  const size_t smem = 2 * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 1) * sizeof(float);
+  const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 1) * sizeof(float);
   delta_rule_kernel<R><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads, kv_heads,
                                                                                            dim, vdim);
   return (int)cudaGetLastError();
@@ -217,7 +228,12 @@ TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, 
   if (taps < 1 || taps > kDeltaMaxTaps || kv_heads < 1 || heads % kv_heads != 0 || 2 * kv_heads > 64) return (int)cudaErrorInvalidValue;
   const int channels = 2 * kv_heads * dim + heads * vdim;
   const size_t smem = (size_t)channels * sizeof(float);
-  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 40 * 1024) {   // beyond what a kernel gets unasked (the static part counts too)
+    const cudaError_t set = dtype == TLIE_F32 ? cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                              : cudaFuncSetAttribute(delta_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (set != cudaSuccess) return (int)set;
+  }
   if (dtype == TLIE_F32)
     delta_prepare_kernel<float><<<tokens, 128, smem, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, taps_w, a_log, dt_bias, state, state_stride,
                                                                conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);

@@ -6,7 +6,7 @@
 //   scale_rows          x *= factor (32-bit, in place)
 //   gather_gated        out[t, d] = act(z[t, d]) * table[ids[t], offset + d]           a slice of a second token table, gated
 //   unit_norm_add       residual[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight        a normalised branch joins the stream
-//   head_linear         out[t, h, :] = W[h] . x[t, h, :]  per head, operands with strides of their own, ascending k in 32-bit
+//   head_linear         out[t, h, :] = W[h] . x[t, h, :]  per head, operands with strides of their own, 32-bit sums in a fixed order
 // Storage float or bfloat16, arithmetic 32-bit.
 #include "common.cuh"
 
@@ -75,19 +75,23 @@ __global__ void unit_norm_add_kernel(float* __restrict__ residual, const T* __re
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) residual[row * hidden + i] += to_float(y[row * hidden + i]) * inv * weight[i];
 }
 
-// out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]: a thread per output, ascending k, so a row's bits depend on the row alone.
+// out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]: a warp per output, the lanes taking k in turns (neighbouring lanes read neighbouring
+// elements) and adding up in a fixed order, so a row's bits depend on the row alone.
 template <typename T>
 __global__ void head_linear_kernel(const T* __restrict__ x, long long x_row, long long x_head, const T* __restrict__ w, T* __restrict__ out, long long out_row,
                                    long long out_head, int heads, int n_out, int k_in, size_t total) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
     const int n = (int)(i % n_out);
     const int h = (int)((i / n_out) % heads);
     const size_t t = i / ((size_t)n_out * heads);
     const T* xr = x + t * x_row + h * x_head;
     const T* wr = w + ((size_t)h * n_out + n) * k_in;
     float sum = 0.0f;
-    for (int k = 0; k < k_in; ++k) sum += to_float(xr[k]) * to_float(wr[k]);
-    out[t * out_row + h * out_head + n] = from_float<T>(sum);
+    for (int k = lane; k < k_in; k += 32) sum += to_float(xr[k]) * to_float(wr[k]);
+    sum = warp_sum(sum);
+    if (lane == 0) out[t * out_row + h * out_head + n] = from_float<T>(sum);
   }
 }
 
@@ -157,7 +161,7 @@ TLIE_EXPORT int tlie_head_linear(int dtype, const void* x, long long x_row, long
                                  int rows, int heads, int n_out, int k_in, cudaStream_t stream) {
   const size_t total = (size_t)rows * heads * n_out;
   if (total == 0) return 0;
-  TLIE_BY_TYPE(dtype, (head_linear_kernel<T><<<blocks_for(total, 128), 128, 0, stream>>>((const T*)x, x_row, x_head, (const T*)w, (T*)out, out_row, out_head, heads,
+  TLIE_BY_TYPE(dtype, (head_linear_kernel<T><<<blocks_for(total * 32, 256), 256, 0, stream>>>((const T*)x, x_row, x_head, (const T*)w, (T*)out, out_row, out_head, heads,
                                                                                        n_out, k_in, total)));
   return (int)cudaGetLastError();
 }

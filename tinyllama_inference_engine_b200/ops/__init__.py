@@ -655,7 +655,11 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
     if pages.dtype != rows.dtype:
         raise KernelError("mixed_heads_attention: pages and rows differ in dtype", code="invalid_dtype")
     table = cache.block_table
-    plain_options = sinks is None and not values_in_keys   # what the tensor-core kernels know
+    if (values_in_keys and window == 0 and gate_offset < 0 and slopes is None and mix is None and rows.shape[1] == heads * key_dim
+            and fast.latent_prefill_takes(batch, rows, key_dim, value_dim)):
+        fast.latent_prefill(rows, batch, table, k_ptr, k_stride, sinks, out, heads, key_dim, value_dim, cache.page_size, scale)
+        return
+    plain_options = sinks is None and not values_in_keys   # what the tensor-core kernels with two planes know
     if plain_options and rows.dtype == torch.bfloat16 and fast.mixed_prefill_takes(batch, rows, cache.page_size, kv_heads if mix is not None else 1, key_dim, value_dim, gate_offset,
                                                                                    gate_per_head):
         folded = folded_slopes if folded_slopes is not None else fast.folded_slopes(slopes, mix)

@@ -43,6 +43,7 @@ def build_all() -> list:
         built.append(build_library(f"tlie_attn_mixed_k{key_dim}_v{value_dim}_p{parts}", ["attention_mixed_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "PARTS": parts}))
         built.append(build_library(f"tlie_attn_mixed_decode_k{key_dim}_v{value_dim}_g{parts}", ["attention_mixed_decode.cu"],
                                    {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "KV_HEADS": parts}))
+    built.append(build_library("tlie_attn_latent_k576_v512", ["attention_latent_prefill.cu"], {"KEY_DIM": 576, "VALUE_DIM": 512}))   # other widths on first use
     return built
 
 
@@ -746,6 +747,38 @@ def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mi
             c_int(heads), c_int(kv_heads), c_int(page_size), c_int(window), c_int(keep_first), c_int(1 if gate_per_head else 0), ops._stream()),
         "mixed_prefill")
     ops.launch_count += 1   # two kernels: the fold and the attention
+
+
+# --- latent attention, prompt portions on the tensor cores -----------------------------------------------------------------------------
+use_latent_prefill = True
+LATENT_PREFILL_MIN_ROWS = 4    # steps whose longest entry has fewer (token, head) row tiles than this many tokens stay on the general kernel
+
+
+def latent_prefill_library(key_dim: int, value_dim: int):
+    """The kernel set of one (cached row width, value width): compiled when a model of these sizes first runs a prompt portion."""
+    return load_library(f"tlie_attn_latent_k{key_dim}_v{value_dim}", ["attention_latent_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim})
+
+
+def latent_prefill_takes(batch, queries, key_dim: int, value_dim: int) -> bool:
+    """Whether attention over one cached row per token (values inside the keys) runs on the tensor-core kernel: bfloat16, a prompt
+    portion among the entries, a row width that is a multiple of 16 and a value width that is a multiple of 32, tiles that fit."""
+    if not use_latent_prefill or batch is None or batch.max_q_len < LATENT_PREFILL_MIN_ROWS or queries.dtype != torch.bfloat16:
+        return False
+    if key_dim % 16 or value_dim % 32 or value_dim > key_dim or batch.num_seqs > 65535 or (64 + 2 * 32) * (key_dim + 8) * 2 > 227 * 1024:
+        return False
+    return latent_prefill_library(key_dim, value_dim).tlie_latent_prefill_fits() == 1
+
+
+def latent_prefill(queries, batch, block_table, pages_ptr, page_stride: int, sinks, out, heads: int, key_dim: int, value_dim: int, page_size: int, scale: float) -> None:
+    """Causal attention of ``heads`` query heads per token over one cached row per token whose first ``value_dim`` columns are the
+    values (csrc/attention_latent_prefill.cu).  ``queries`` [T, heads * key_dim], ``out`` [T, heads * value_dim]."""
+    ops = _ops()
+    ops._check(
+        latent_prefill_library(key_dim, value_dim).tlie_latent_prefill(
+            ops._ptr(queries), pages_ptr, c_longlong(page_stride), ops._i32(batch.seq_starts, "seq_starts"), ops._i32(batch.first_positions, "first_positions"),
+            ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(sinks), ops._ptr(out), c_int(queries.shape[0]), c_int(batch.num_seqs),
+            c_int(batch.max_q_len), c_int(heads), c_int(page_size), c_float(scale), ops._stream()),
+        "latent_prefill")
 
 
 # --- attention with mixed heads, steps of few rows on the tensor cores ------------------------------------------------------------------
