@@ -166,7 +166,7 @@ def test_cache_groups_and_kept_pages():
     manager = CacheManager(needs, page_size=16, num_pages=40, max_requests=2, max_positions=4096)
     groups = [(g.need.window, g.need.keep_first, g.need.page_planes(), len(g.streams)) for g in manager.page_groups]
     assert groups == [(20, 3, ((2, 16), (2, 16)), 1), (0, 0, ((1, 40),), 3), (16, 0, ((2, 32), (2, 32)), 1)]
-    assert [(g.need.state_shape, len(g.streams)) for g in manager.state_groups] == [((4 * 24 * 16 + 2 * (2 * 2 * 24 + 4 * 16),), 3)]
+    assert [(g.need.state_shape, len(g.streams)) for g in manager.state_groups] == [((4 * 32 * 16 + 2 * (2 * 2 * 24 + 4 * 16),), 3)]      # the matrices' key channels padded to 32
     manager.admit("a")
     manager.reserve("a", 100)
     manager.advance("a", 100)

@@ -11,6 +11,10 @@
 // maximum and sum; each multiplies the weights with its half of the value columns, the accumulators (16 x VALUE_DIM / 2 per warp)
 // staying in registers.  Keys stream through a ring of 32-key tiles (cp.async).
 //
+// Steps of few rows (decoded tokens): gridDim.z CTAs share a row tile's key tiles; each leaves its unnormalised sums, maxima and
+// totals in ``partial`` ([token][part][heads * VALUE_DIM + 2 heads], as the general kernel's parts) and a merge kernel puts them
+// together and adds the sink.
+//
 // Compile-time: KEY_DIM (a multiple of 16), VALUE_DIM (a multiple of 32, at most KEY_DIM).
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -36,7 +40,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 __global__ void __launch_bounds__(kThreads, 1)
     latent_prefill_kernel(const __nv_bfloat16* __restrict__ queries, const __nv_bfloat16* __restrict__ pages, long long page_stride, const int* __restrict__ seq_starts,
                           const int* __restrict__ first_positions, const int* __restrict__ block_table, int table_stride, const float* __restrict__ sinks,
-                          __nv_bfloat16* __restrict__ out, int heads, int page_size, float scale) {
+                          __nv_bfloat16* __restrict__ out, int heads, int page_size, float scale, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][kRow]
   __nv_bfloat16* k_ring = q_smem + (size_t)kRows * kRow;                // [kStages][32][kRow]
@@ -60,10 +64,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool valid = row < rows_here;
     cp_async_16(q_smem + (size_t)row * kRow + chunk * 8, queries + (row0 + (valid ? row : 0)) * kD + chunk * 8, valid);
   }
-  const int tiles = (n_keys + kKeys - 1) / kKeys;
+  const int all_tiles = (n_keys + kKeys - 1) / kKeys;
+  const int tiles_each = (all_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int tile0 = blockIdx.z * tiles_each, tiles = min(all_tiles, tile0 + tiles_each);   // this CTA's tiles: [tile0, tiles)
   auto issue = [&](int tile) {
     if (tile < tiles) {
-      __nv_bfloat16* dst = k_ring + (size_t)(tile % kStages) * kKeys * kRow;
+      __nv_bfloat16* dst = k_ring + (size_t)((tile - tile0) % kStages) * kKeys * kRow;
       for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kThreads) {
         const int row = idx / kChunks, chunk = idx - row * kChunks;
         const int key = tile * kKeys + row;
@@ -75,7 +81,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     cp_async_commit();   // a group per tile, empty past the end
   };
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue(s);   // the first group also holds the queries
+  for (int s = 0; s < kStages - 1; ++s) issue(tile0 + s);   // the first group also holds the queries
 
   const int my_row[2] = {tile_m * 16 + g, tile_m * 16 + g + 8};
   int my_pos[2];
@@ -90,11 +96,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0f, 0.0f};
 
-  for (int tile = 0; tile < tiles; ++tile) {
+  for (int tile = tile0; tile < tiles; ++tile) {
     cp_async_wait<kStages - 2>();   // this thread's copies of this tile have landed ...
     __syncthreads();                // ... and everyone's; and everyone is done with the tile before, whose buffer is written next
     issue(tile + kStages - 1);
-    const __nv_bfloat16* k_smem = k_ring + (size_t)(tile % kStages) * kKeys * kRow;
+    const __nv_bfloat16* k_smem = k_ring + (size_t)((tile - tile0) % kStages) * kKeys * kRow;
     const int key0 = tile * kKeys;
     if (key0 > warp_last_pos) continue;   // no row of this warp sees a key of this tile (nor of any later one)
     float s_frag[kKeys / 8][4];
@@ -178,6 +184,27 @@ __global__ void __launch_bounds__(kThreads, 1)
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
   }
 #pragma unroll
+  if (partial != nullptr) {
+    const int outputs = heads * kVD;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (my_row[r] >= rows_here) continue;
+      const size_t row = row0 + my_row[r];
+      const int h = (int)(row % heads);
+      float* mine = partial + ((row / heads) * gridDim.z + blockIdx.z) * ((size_t)outputs + 2 * heads);
+#pragma unroll
+      for (int i = 0; i < kHalf / 8; ++i) {
+        mine[h * kVD + half * kHalf + i * 8 + 2 * t] = o[i][r * 2];
+        mine[h * kVD + half * kHalf + i * 8 + 2 * t + 1] = o[i][r * 2 + 1];
+      }
+      if (half == 0 && t == 0) {
+        mine[outputs + h] = row_max[r] * 0.6931471805599453f;   // the parts' maxima are kept in natural units
+        mine[outputs + heads + h] = row_sum[r];
+      }
+    }
+    return;
+  }
+#pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (my_row[r] >= rows_here) continue;
     const size_t row = row0 + my_row[r];
@@ -199,11 +226,13 @@ TLIE_EXPORT int tlie_latent_prefill_fits() { return kFits ? 1 : 0; }
 
 // ``queries`` bfloat16 [tokens * heads, KEY_DIM]; ``pages`` [page][slot][KEY_DIM] with ``page_stride`` elements between pages; ``out``
 // bfloat16 [tokens * heads, VALUE_DIM]; ``sinks`` 32-bit [heads] or null; ``longest``: the most rows any entry of the step has.
+// ``splits`` > 1: that many CTAs share a row tile's keys and write ``partial`` (tokens * splits * (heads * VALUE_DIM + 2 * heads) floats)
+// instead of ``out``; the caller merges the parts (and adds the sinks there).
 TLIE_EXPORT int tlie_latent_prefill(const void* queries, const void* pages, long long page_stride, const int* seq_starts, const int* first_positions,
                                     const int* block_table, int table_stride, const float* sinks, void* out, int tokens, int entries, int longest, int heads,
-                                    int page_size, float scale, cudaStream_t stream) {
+                                    int page_size, float scale, int splits, float* partial, cudaStream_t stream) {
   if (tokens <= 0 || entries <= 0) return 0;
-  if (!kFits || heads <= 0 || entries > 65535 || page_size <= 0) return (int)cudaErrorInvalidValue;
+  if (!kFits || heads <= 0 || entries > 65535 || page_size <= 0 || splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
   constexpr size_t smem = smem_with(kStages);
   static bool configured = false;
   if (!configured) {
@@ -211,8 +240,8 @@ TLIE_EXPORT int tlie_latent_prefill(const void* queries, const void* pages, long
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const dim3 grid(((size_t)longest * heads + kRows - 1) / kRows, entries);
+  const dim3 grid(((size_t)longest * heads + kRows - 1) / kRows, entries, splits);
   latent_prefill_kernel<<<grid, kThreads, smem, stream>>>((const __nv_bfloat16*)queries, (const __nv_bfloat16*)pages, page_stride, seq_starts, first_positions,
-                                                          block_table, table_stride, sinks, (__nv_bfloat16*)out, heads, page_size, scale);
+                                                          block_table, table_stride, sinks, (__nv_bfloat16*)out, heads, page_size, scale, splits > 1 ? partial : nullptr);
   return (int)cudaGetLastError();
 }

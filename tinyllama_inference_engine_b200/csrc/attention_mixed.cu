@@ -595,3 +595,12 @@ TLIE_EXPORT int tlie_latent_store(int dtype, const void* rows, int row_stride, i
                                                                    write_cache, (__nv_bfloat16*)queries);
   return (int)cudaGetLastError();
 }
+
+// The merge alone, for a kernel of another file that leaves a row's parts in the same layout (bfloat16 output, no gate).
+TLIE_EXPORT int tlie_merge_parts(const float* partial, void* out, int tokens, int heads, int value_dim, int splits, const float* sinks, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (splits < 1 || splits > 64) return (int)cudaErrorInvalidValue;
+  merge_mixed_kernel<__nv_bfloat16><<<dim3(tokens, heads), value_dim >= 128 ? 128 : (value_dim > 32 ? 64 : 32), 0, stream>>>(partial, nullptr, 0, -1, (__nv_bfloat16*)out, heads,
+                                                                                                                          value_dim, splits, 0, sinks);
+  return (int)cudaGetLastError();
+}

@@ -8,16 +8,17 @@
 // together by shuffles) and one pass of updates.  o is worked out as q . (g S)_j + (q . k) u_j.
 //
 // Kernels:
-//   delta_prepare    per token: the short causal convolution of q, k, v over time (the taps before an entry's first row come
+//   delta_prepare    per (token, head): the short causal convolution of q, k, v over time (the taps before an entry's first row come
 //                    from the request's convolution state) with silu, unit norms of q and k per head, q's scale,
 //                    beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)): all 32-bit, into one row of ``prep``
 //   delta_conv_state per entry: the last taps - 1 inputs of the convolution, kept for the next step
-//   delta_rule       the recurrence: one CTA per (entry, head, 16 columns), rows in order, the operands of the next seven rows
-//                    on their way (asynchronous copies into a ring) while the current one is worked on
+//   delta_rule       the recurrence: one CTA per (entry, head, 16 columns), rows in order, the operands of the next twelve rows
+//                    on their way (asynchronous copies into a ring of 16) while a block of four is worked on between two barriers
 //   delta_gate_norm  per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
 //
 // State of a request (32-bit words): for every head the matrix in the order the recurrence reads it,
-// [(dim + 7) / 8][vdim][8] (key channel 8 i + l at [i][j][l]), then the convolution's inputs [taps - 1][channels].
+// [4 ceil(dim / 32)][vdim][8] (lane l of a column's 8 holds key channels 32 (i / 4) + 4 l + i % 4 at [i][j][l]: four neighbours per
+// 16-byte read of the staged operands), then the convolution's inputs [taps - 1][channels].
 #include "common.cuh"
 
 namespace tlie {
@@ -31,45 +32,56 @@ __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
 // prep row: [q: G dim | k: G dim | v: H vdim | beta: H | decay: H dim]
+// One CTA per (token, head): blockIdx.y < 2 G is a q head (then a k head): convolution, silu, unit norm (q also scaled); the others are
+// the value heads: convolution and silu, and beside them the head's beta and its dim decays.  Few rows (decoded tokens) then still
+// fill the SMs, and a thread's loads (the taps of one channel) do not wait for one another.
 template <typename T>
 __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict__ rows, int row_stride, int beta_offset, const T* __restrict__ a, const float* __restrict__ taps_w,
                                                             const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                                                             long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
                                                             const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep,
                                                             int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale) {
-  extern __shared__ float conv_s[];   // [channels] the convolved and activated q, k, v of this token
-  __shared__ float inv_s[64];         // 1 / norm of every q and k head
-  const int t = blockIdx.x;
+  __shared__ float conv_s[256];   // the convolved and activated channels of a q or k head (dim <= 256)
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, part = blockIdx.y;
   const int entry = token_seq[t];
   const int first = seq_starts[entry];
   const int r = t - first;
   const int qk = kv_heads * dim;
   const int channels = 2 * qk + heads * vdim;
   const float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  const int width = channels + heads + heads * dim;
+  float* out = prep + (size_t)t * width;
+  const bool unit = part < 2 * kv_heads;
+  const int c0 = unit ? part * dim : 2 * qk + (part - 2 * kv_heads) * vdim;
+  const int count = unit ? dim : vdim;
+  float squares = 0.0f;
+  for (int d = threadIdx.x; d < count; d += blockDim.x) {
+    const int c = c0 + d;
     float sum = 0.0f;
     for (int j = 0; j < taps; ++j) {
       const int back = r - (taps - 1) + j;   // row of the entry this tap reads; negative: before this step
       const float x = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
       sum += taps_w[c * taps + j] * x;
     }
-    conv_s[c] = sum * sigmoid_f(sum);
+    const float y = sum * sigmoid_f(sum);
+    if (unit) {
+      conv_s[d] = y;
+      squares += y * y;
+    } else {
+      out[c] = y;
+    }
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int h = warp; h < 2 * kv_heads; h += warps) {   // q heads then k heads
-    float squares = 0.0f;
-    for (int d = lane; d < dim; d += 32) squares += conv_s[h * dim + d] * conv_s[h * dim + d];
-    squares = warp_sum(squares);
-    if (lane == 0) inv_s[h] = (1.0f / sqrtf(squares + unit_eps)) * (h < kv_heads ? q_scale : 1.0f);
+  if (unit) {
+    const float inv = (1.0f / sqrtf(block_sum(squares, scratch) + unit_eps)) * (part < kv_heads ? q_scale : 1.0f);
+    for (int d = threadIdx.x; d < count; d += blockDim.x) out[c0 + d] = conv_s[d] * inv;   // a thread reads back what it wrote itself
+    return;
   }
-  __syncthreads();
-  const int width = 2 * qk + heads * vdim + heads + heads * dim;
-  float* out = prep + (size_t)t * width;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) out[c] = c < 2 * qk ? conv_s[c] * inv_s[c / dim] : conv_s[c];
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) out[channels + h] = sigmoid_f(to_float(rows[(size_t)t * row_stride + beta_offset + h]));
-  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
-    const float rate = expf(a_log[i / dim]);
+  const int h = part - 2 * kv_heads;
+  if (threadIdx.x == 0) out[channels + h] = sigmoid_f(to_float(rows[(size_t)t * row_stride + beta_offset + h]));
+  const float rate = expf(a_log[h]);
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const int i = h * dim + d;
     out[channels + heads + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * heads * dim + i]) + dt_bias[i]));
   }
 }
@@ -90,7 +102,8 @@ __global__ void delta_conv_state_kernel(const T* __restrict__ rows, int row_stri
   for (int i = 0; i < taps - 1; ++i) conv_state[(size_t)i * channels + c] = keep[i];
 }
 
-constexpr int kDeltaStages = 8;   // rows whose operands are in flight or staged ahead of the one being worked on
+constexpr int kDeltaStages = 16;   // rows whose operands are in flight or staged ahead of the one being worked on
+constexpr int kDeltaBlock = 4;     // rows between two barriers: their copies are one group, and the compiler may overlap their work
 
 __device__ __forceinline__ void delta_copy_word(float* dst, const float* src) {
   const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
@@ -100,16 +113,16 @@ __device__ __forceinline__ void delta_commit() { asm volatile("cp.async.commit_g
 template <int N>
 __device__ __forceinline__ void delta_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// R: key channels a lane has registers for (dim <= 8 R); the state holds ceil(dim / 8) of them per lane.
+// R: key channels a lane has registers for (a multiple of 4, dim <= 8 R); the state holds 4 ceil(dim / 32) of them per lane.
 // A row's operands ([q | k | g] of the head, the CTA's 16 values, beta) are copied asynchronously into a ring of kDeltaStages
 // buffers, several rows ahead, so that a row's turn never waits for memory; padding words are zeroed once and never copied.
 template <int R>
 __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
                                                                   int heads, int kv_heads, int dim, int vdim) {
-  extern __shared__ float stage_s[];   // kDeltaStages buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta]
+  extern __shared__ __align__(16) float stage_s[];   // kDeltaStages buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta | 3 unused]
   constexpr int kPadded = kDeltaLanes * R;
-  constexpr int kRow = 3 * kPadded + kDeltaColumns + 1;
+  constexpr int kRow = 3 * kPadded + kDeltaColumns + 4;
   constexpr int kLoads = (kRow + kDeltaThreads - 1) / kDeltaThreads;
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
   const int head = blockIdx.x / column_blocks, block = blockIdx.x - head * column_blocks;
@@ -120,7 +133,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   const int kv = head / (heads / kv_heads);
   const int qk = kv_heads * dim;
   const int width = 2 * qk + heads * vdim + heads + heads * dim;
-  const int held = (dim + kDeltaLanes - 1) / kDeltaLanes;   // key channels per lane that exist (and are stored)
+  const int held = 4 * ((dim + 31) / 32);   // key channels per lane that are stored
   const size_t matrix = (size_t)held * vdim * kDeltaLanes;
   float* mine = state + (size_t)state_slots[entry] * state_stride + (size_t)head * matrix;
 
@@ -143,46 +156,65 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
 #pragma unroll
   for (int i = 0; i < R; ++i) S[i] = (live && i < held) ? mine[((size_t)i * vdim + column) * kDeltaLanes + lane] : 0.0f;
 
-  auto issue = [&](int row) {   // one group per row, empty past the end, so that the count of groups in flight is the same at every step
-    if (row < count) {
-      const float* from = prep + (size_t)(first + row) * width;
-      float* to = stage_s + (row % kDeltaStages) * kRow;
+  auto issue = [&](int block_of_rows) {   // one group per block of rows, empty past the end, so that the count of groups in flight is the same at every step
 #pragma unroll
-      for (int i = 0; i < kLoads; ++i)
-        if (source[i] >= 0) delta_copy_word(to + tid + i * kDeltaThreads, from + source[i]);
+    for (int n = 0; n < kDeltaBlock; ++n) {
+      const int row = block_of_rows * kDeltaBlock + n;
+      if (row < count) {
+        const float* from = prep + (size_t)(first + row) * width;
+        float* to = stage_s + (row % kDeltaStages) * kRow;
+#pragma unroll
+        for (int i = 0; i < kLoads; ++i)
+          if (source[i] >= 0) delta_copy_word(to + tid + i * kDeltaThreads, from + source[i]);
+      }
     }
     delta_commit();
   };
+  constexpr int kBlocksAhead = kDeltaStages / kDeltaBlock - 1;
 #pragma unroll
-  for (int ahead = 0; ahead < kDeltaStages - 1; ++ahead) issue(ahead);
-  for (int row = 0; row < count; ++row) {
-    delta_wait<kDeltaStages - 2>();   // this thread's copies of this row have landed ...
-    __syncthreads();                  // ... and so have everyone's; and everyone is done with the row before, whose buffer is written next
-    issue(row + kDeltaStages - 1);
-    const float* cur = stage_s + (row % kDeltaStages) * kRow;
-    float reach = 0.0f, read = 0.0f, both = 0.0f;   // k . (g S)_j, q . (g S)_j, q . k  (this lane's share)
-    float kk[R];
+  for (int ahead = 0; ahead < kBlocksAhead; ++ahead) issue(ahead);
+  const int blocks = (count + kDeltaBlock - 1) / kDeltaBlock;
+  for (int block_of_rows = 0; block_of_rows < blocks; ++block_of_rows) {
+    delta_wait<kBlocksAhead - 1>();   // this thread's copies of this block's rows have landed ...
+    __syncthreads();                  // ... and so have everyone's; and everyone is done with the block before, whose buffers are written next
+    issue(block_of_rows + kBlocksAhead);
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int d = lane + kDeltaLanes * i;
-      const float q = cur[d], k = cur[kPadded + d], g = cur[2 * kPadded + d];
-      S[i] *= g;
-      reach += k * S[i];
-      read += q * S[i];
-      both += q * k;
-      kk[i] = k;
+    for (int n = 0; n < kDeltaBlock; ++n) {
+      const int row = block_of_rows * kDeltaBlock + n;
+      if (row >= count) break;
+      const float* cur = stage_s + (row % kDeltaStages) * kRow;
+      // k . (g S)_j, q . (g S)_j, q . k (this lane's share), each in two chains of sums
+      float reach2[2] = {0.0f, 0.0f}, read2[2] = {0.0f, 0.0f}, both2[2] = {0.0f, 0.0f};
+      float kk[R];
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 32 + lane * 4);
+        const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 32 + lane * 4);
+        const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 32 + lane * 4);
+        const float q[4] = {q4.x, q4.y, q4.z, q4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w}, g[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int i = 4 * j + c;
+          S[i] *= g[c];
+          reach2[c & 1] += k[c] * S[i];
+          read2[c & 1] += q[c] * S[i];
+          both2[c & 1] += q[c] * k[c];
+          kk[i] = k[c];
+        }
+      }
+      float reach = reach2[0] + reach2[1], read = read2[0] + read2[1], both = both2[0] + both2[1];
+#pragma unroll
+      for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1) {
+        reach += __shfl_xor_sync(0xffffffffu, reach, offset);
+        read += __shfl_xor_sync(0xffffffffu, read, offset);
+        both += __shfl_xor_sync(0xffffffffu, both, offset);
+      }
+      const float v = cur[3 * kPadded + (tid / kDeltaLanes)], beta = cur[3 * kPadded + kDeltaColumns];
+      const float u = beta * (v - reach);
+#pragma unroll
+      for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
+      if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
     }
-#pragma unroll
-    for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1) {
-      reach += __shfl_xor_sync(0xffffffffu, reach, offset);
-      read += __shfl_xor_sync(0xffffffffu, read, offset);
-      both += __shfl_xor_sync(0xffffffffu, both, offset);
-    }
-    const float v = cur[3 * kPadded + (tid / kDeltaLanes)], beta = cur[3 * kPadded + kDeltaColumns];
-    const float u = beta * (v - reach);
-#pragma unroll
-    for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
-    if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
   }
   delta_wait<0>();
   if (live && count > 0) {
@@ -210,7 +242,7 @@ template <int R>
 static int launch_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
                              int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
-  const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 1) * sizeof(float);
+  const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 4) * sizeof(float);
   delta_rule_kernel<R><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads, kv_heads,
                                                                                            dim, vdim);
   return (int)cudaGetLastError();
@@ -225,22 +257,17 @@ TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, 
                                    const int* state_slots, float* prep, int tokens, int entries, int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps,
                                    float q_scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (taps < 1 || taps > kDeltaMaxTaps || kv_heads < 1 || heads % kv_heads != 0 || 2 * kv_heads > 64) return (int)cudaErrorInvalidValue;
+  if (taps < 1 || taps > kDeltaMaxTaps || kv_heads < 1 || heads % kv_heads != 0 || 2 * kv_heads + heads > 65535) return (int)cudaErrorInvalidValue;
   const int channels = 2 * kv_heads * dim + heads * vdim;
-  const size_t smem = (size_t)channels * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  if (smem > 40 * 1024) {   // beyond what a kernel gets unasked (the static part counts too)
-    const cudaError_t set = dtype == TLIE_F32 ? cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                              : cudaFuncSetAttribute(delta_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (set != cudaSuccess) return (int)set;
-  }
+  if (dim > 256) return (int)cudaErrorInvalidValue;
+  const dim3 parts(tokens, 2 * kv_heads + heads);
   if (dtype == TLIE_F32)
-    delta_prepare_kernel<float><<<tokens, 128, smem, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, taps_w, a_log, dt_bias, state, state_stride,
-                                                               conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);
+    delta_prepare_kernel<float><<<parts, 128, 0, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, taps_w, a_log, dt_bias, state, state_stride,
+                                                           conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);
   else
-    delta_prepare_kernel<__nv_bfloat16><<<tokens, 128, smem, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, taps_w, a_log, dt_bias,
-                                                                       state, state_stride, conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim,
-                                                                       vdim, taps, unit_eps, q_scale);
+    delta_prepare_kernel<__nv_bfloat16><<<parts, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, taps_w, a_log, dt_bias,
+                                                                   state, state_stride, conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim,
+                                                                   vdim, taps, unit_eps, q_scale);
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess || taps == 1) return (int)status;
   const dim3 grid((channels + 127) / 128, entries);
@@ -256,7 +283,7 @@ TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state
                                 int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   if (entries <= 0) return 0;
   if (dim < 1 || dim > 256 || kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
-  const int r = (dim + kDeltaLanes - 1) / kDeltaLanes;
+  const int r = 4 * ((dim + 31) / 32);
 #define TLIE_DELTA(R) \
   if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream)
   TLIE_DELTA(4);

@@ -43,6 +43,29 @@ __global__ void clamped_gate_mul_kernel(const T* __restrict__ gate_up, T* __rest
   }
 }
 
+// the same, eight bfloat16 elements per thread (inter a multiple of 8): 16-byte loads and stores
+__global__ void clamped_gate_mul_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, size_t total8, float limit, float alpha,
+                                            float shift) {
+  const int per_row = inter / 8;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / per_row, col = (i - row * per_row) * 8;
+    const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + col);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + inter + col);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 result;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const float2 g2 = __bfloat1622float2(gp[n]), u2 = __bfloat1622float2(up[n]);
+      const float g0 = fminf(g2.x, limit), g1 = fminf(g2.y, limit);
+      const float u0 = fminf(fmaxf(u2.x, -limit), limit), u1 = fminf(fmaxf(u2.y, -limit), limit);
+      rp[n] = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + expf(-alpha * g0))) * (u0 + shift), g1 * (1.0f / (1.0f + expf(-alpha * g1))) * (u1 + shift));
+    }
+    *reinterpret_cast<uint4*>(out + row * inter + col) = result;
+  }
+}
+
 __global__ void scale_rows_kernel(float* __restrict__ x, float factor, size_t total) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] *= factor;
 }
@@ -61,18 +84,31 @@ __global__ void gather_gated_kernel(const T* __restrict__ z, const T* __restrict
   }
 }
 
-// one CTA per row
+// one CTA per row; a thread keeps its (up to 16) elements of y in registers between the sum of squares and the add
 template <typename T>
 __global__ void unit_norm_add_kernel(float* __restrict__ residual, const T* __restrict__ y, const float* __restrict__ weight, float eps, int hidden) {
   __shared__ float scratch[32];
+  constexpr int kKept = 16;
   const size_t row = blockIdx.x;
+  float kept[kKept];
   float squares = 0.0f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+#pragma unroll
+  for (int n = 0; n < kKept; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    kept[n] = i < hidden ? to_float(y[row * hidden + i]) : 0.0f;
+    squares += kept[n] * kept[n];
+  }
+  for (int i = threadIdx.x + kKept * blockDim.x; i < hidden; i += blockDim.x) {
     const float v = to_float(y[row * hidden + i]);
     squares += v * v;
   }
   const float inv = rsqrtf(block_sum(squares, scratch) / (float)hidden + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) residual[row * hidden + i] += to_float(y[row * hidden + i]) * inv * weight[i];
+#pragma unroll
+  for (int n = 0; n < kKept; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    if (i < hidden) residual[row * hidden + i] += kept[n] * inv * weight[i];
+  }
+  for (int i = threadIdx.x + kKept * blockDim.x; i < hidden; i += blockDim.x) residual[row * hidden + i] += to_float(y[row * hidden + i]) * inv * weight[i];
 }
 
 // out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]: a warp per output, the lanes taking k in turns (neighbouring lanes read neighbouring
@@ -130,6 +166,10 @@ TLIE_EXPORT int tlie_complete_and_round(int dtype, float* residual, const void* 
 TLIE_EXPORT int tlie_clamped_gate_mul(int dtype, const void* gate_up, void* out, int rows, int inter, float limit, float alpha, float shift, cudaStream_t stream) {
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
+  if (dtype == TLIE_BF16 && inter % 8 == 0) {
+    clamped_gate_mul_vec_kernel<<<blocks_for(total / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total / 8, limit, alpha, shift);
+    return (int)cudaGetLastError();
+  }
   TLIE_BY_TYPE(dtype, (clamped_gate_mul_kernel<T><<<blocks_for(total, 256), 256, 0, stream>>>((const T*)gate_up, (T*)out, inter, total, limit, alpha, shift)));
   return (int)cudaGetLastError();
 }
@@ -152,7 +192,7 @@ TLIE_EXPORT int tlie_gather_gated(int dtype, const void* z, const void* table, c
 
 TLIE_EXPORT int tlie_unit_norm_add(int dtype, float* residual, const void* y, const float* weight, float eps, int rows, int hidden, cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0) return 0;
-  const int threads = hidden >= 1024 ? 256 : 128;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128);
   TLIE_BY_TYPE(dtype, (unit_norm_add_kernel<T><<<rows, threads, 0, stream>>>(residual, (const T*)y, weight, eps, hidden)));
   return (int)cudaGetLastError();
 }

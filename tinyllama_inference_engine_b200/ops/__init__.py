@@ -493,7 +493,7 @@ def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_ro
                                         _i32(state_slots, "state_slots"), _ptr(out), c_int(entries), c_int(width), c_int(runs), _stream()), "mingru_scan")
 
 
-DELTA_LANES = 8   # lanes that share a column of the delta rule's state: the matrix is stored [ceil(dim / 8)][vdim][8] per head
+DELTA_LANES = 8   # lanes that share a column of the delta rule's state: the matrix is stored [4 ceil(dim / 32)][vdim][8] per head
 
 
 def delta_rule_library():
@@ -502,7 +502,7 @@ def delta_rule_library():
 
 def delta_state_words(heads: int, dim: int, vdim: int, channels: int, taps: int) -> tuple[int, int]:
     """(words of a request's delta-rule state, where the convolution's inputs start in it): the heads' matrices, then taps - 1 rows of inputs."""
-    matrices = heads * (-(-dim // DELTA_LANES)) * DELTA_LANES * vdim
+    matrices = heads * 4 * (-(-dim // 32)) * DELTA_LANES * vdim
     return matrices + (taps - 1) * channels, matrices
 
 

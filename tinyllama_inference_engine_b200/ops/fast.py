@@ -751,7 +751,7 @@ def mixed_prefill(rows, gate_offset: int, batch, block_table, planes, folded, mi
 
 # --- latent attention, prompt portions on the tensor cores -----------------------------------------------------------------------------
 use_latent_prefill = True
-LATENT_PREFILL_MIN_ROWS = 4    # steps whose longest entry has fewer (token, head) row tiles than this many tokens stay on the general kernel
+LATENT_PREFILL_MIN_ROWS = 1    # the longest entry's tokens from which a step runs on the tensor-core kernel (steps of single tokens split their keys)
 
 
 def latent_prefill_library(key_dim: int, value_dim: int):
@@ -771,14 +771,26 @@ def latent_prefill_takes(batch, queries, key_dim: int, value_dim: int) -> bool:
 
 def latent_prefill(queries, batch, block_table, pages_ptr, page_stride: int, sinks, out, heads: int, key_dim: int, value_dim: int, page_size: int, scale: float) -> None:
     """Causal attention of ``heads`` query heads per token over one cached row per token whose first ``value_dim`` columns are the
-    values (csrc/attention_latent_prefill.cu).  ``queries`` [T, heads * key_dim], ``out`` [T, heads * value_dim]."""
+    values (csrc/attention_latent_prefill.cu).  ``queries`` [T, heads * key_dim], ``out`` [T, heads * value_dim].  A step whose CTAs
+    would leave most SMs empty (decoded tokens: one row tile per request) deals every row tile's keys to several CTAs, down to four
+    tiles of 32 keys each, and merges the parts with the general kernel's merge."""
     ops = _ops()
+    tokens = queries.shape[0]
+    row_tiles = -(-batch.max_q_len * heads // 64) * batch.num_seqs
+    splits, partial = 1, None
+    if 2 * row_tiles <= sm_count():
+        splits = max(1, min(sm_count() // row_tiles, -(-batch.max_seq_len // 128), 64))
+    if splits > 1:
+        partial = mixed_scratch(queries.device, tokens * splits * (heads * value_dim + 2 * heads), torch.float32)
     ops._check(
         latent_prefill_library(key_dim, value_dim).tlie_latent_prefill(
             ops._ptr(queries), pages_ptr, c_longlong(page_stride), ops._i32(batch.seq_starts, "seq_starts"), ops._i32(batch.first_positions, "first_positions"),
             ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(sinks), ops._ptr(out), c_int(queries.shape[0]), c_int(batch.num_seqs),
-            c_int(batch.max_q_len), c_int(heads), c_int(page_size), c_float(scale), ops._stream()),
+            c_int(batch.max_q_len), c_int(heads), c_int(page_size), c_float(scale), c_int(splits), ops._ptr(partial), ops._stream()),
         "latent_prefill")
+    if splits > 1:
+        ops._check(ops.mixed_attention().tlie_merge_parts(ops._ptr(partial), ops._ptr(out), c_int(tokens), c_int(heads), c_int(value_dim), c_int(splits), ops._ptr(sinks),
+                                                          ops._stream()), "merge_parts")
 
 
 # --- attention with mixed heads, steps of few rows on the tensor cores ------------------------------------------------------------------
