@@ -65,9 +65,11 @@ CONFIGS = {
     "attention_only": (_config(32, 50, [_attention(4, 4, 8, 7, 2), _attention(2, 1, 16, 0, 0, mlp=16), _attention(3, 1, 16, 40, 17)]), 4),
     "latent_only": (_config(32, 50, [_latent(4, 8, 16, 8, 32, mlp=16), _latent(2, 24, 4, 12, 40)]), 6),
     "delta_only": (_config(32, 50, [_delta(2, 2, 16, 16, 4), _delta(6, 2, 12, 20, 3, mlp=16), _delta(1, 1, 72, 40, 1)], side=16), 7),
+    # nothing a multiple of 8: the width, the vocabulary, the feed-forwards, the heads' widths, the low ranks, the token slice
+    "odd": (_config(44, 37, [_latent(3, 12, 6, 10, 20, mlp=50), _attention(2, 2, 12, 9, 1), _delta(3, 1, 10, 6, 2, mlp=26, ranks=(5, 3))], loop=(1, 2, 2), side=3), 8),
 }
 LENGTHS = {"all": [1, 9, 70, 150, 33, 64, 17], "plain_order": [2, 130, 65, 16, 200], "whole_loop": [3, 40, 100, 64, 7], "attention_only": [90, 5, 48, 17],
-           "latent_only": [75, 1, 130, 16], "delta_only": [200, 5, 66, 2]}
+           "latent_only": [75, 1, 130, 16], "delta_only": [200, 5, 66, 2], "odd": [70, 3, 33, 18]}
 TOLERANCE = {"float32": 3e-5, "bfloat16": 2.5e-2}     # 32-bit: of a row's largest difference; bfloat16: of its root mean square over the vocabulary
 RMS = {"float32": False, "bfloat16": True}             # (these models amplify rounding noise: single logits of a bfloat16 row stray several times further)
 
@@ -477,3 +479,38 @@ def test_generation_in_bfloat16_runs_and_repeats(folders):
     first = generate(folders["plain_order"], prompts, max_tokens=24, dtype="bfloat16", page_size=16, max_cache_tokens=1024, max_requests=4, max_batch_tokens=64)
     second = generate(folders["plain_order"], prompts, max_tokens=24, dtype="bfloat16", page_size=16, max_cache_tokens=1024, max_requests=4, max_batch_tokens=64)
     assert first == second and all(len(tokens) == 24 for tokens in first)
+
+
+@pytest.mark.gpu
+def test_command_line_and_feed_forward_of_few_rows(folders, capsys):
+    """The framework's command line generates with a Zirutar folder and prints its logits; a decode step's feed-forward (the clamped gate in
+    the product's epilogue, up to 16 rows) gives what a prompt portion's does (a kernel of its own behind the product)."""
+    from tinyllama_inference_engine_b200 import ops
+    from tinyllama_inference_engine_b200.cli import main
+
+    folder = folders["all"]
+    config, tensors = load_plain(folder)
+    prompt = [int(t) for t in np.random.default_rng(12).integers(0, config["vocab"], size=11)]
+    text = ",".join(map(str, prompt))
+    assert main(["generate", str(folder), text, "6", "--dtype", "float32", "--page-size", "16"]) == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert result["generated_tokens"] == _plain_greedy(config, tensors, prompt, 6) and result["prompt_tokens"] == 11
+    assert main(["logits", str(folder), text, "--dtype", "float32"]) == 0
+    logits = torch.tensor(json.loads(capsys.readouterr().out)["logits"])
+    assert torch.allclose(logits, plain_zirutar.forward(config, tensors, prompt)[-1], atol=3e-5 * float(logits.abs().max()))
+    g = torch.Generator().manual_seed(5)
+    weight = (torch.randn(2 * 72, 64, generator=g) * 0.3).bfloat16().cuda()
+    for rows in (1, 7, 16):
+        x = torch.randn(rows, 64, generator=g).bfloat16().cuda()
+        gate_up = torch.zeros(rows, 144, dtype=torch.bfloat16, device="cuda")
+        want, got = torch.zeros(rows, 72, dtype=torch.bfloat16, device="cuda"), torch.zeros(rows, 72, dtype=torch.bfloat16, device="cuda")
+        ops.linear(x, weight, gate_up)
+        ops.clamped_gate_mul(gate_up, want, 0.8, 1.702, 1.0)
+        before = ops.launch_count
+        ops.linear_gated(x, weight, got, clamp=(0.8, 1.702, 1.0))
+        assert ops.launch_count - before == 1
+        assert torch.allclose(got.float(), want.float(), atol=1e-2, rtol=1e-2)
+        reference = x.float().cpu() @ weight.float().cpu().T
+        plain = torch.clamp(reference[:, :72], max=0.8)
+        plain = plain * torch.sigmoid(1.702 * plain) * (torch.clamp(reference[:, 72:], -0.8, 0.8) + 1.0)
+        assert torch.allclose(got.float().cpu(), plain, atol=3e-2, rtol=3e-2)

@@ -34,6 +34,10 @@ struct GemvArgs {
   // STORE_BF16 may apply an activation to the (rounded) product before it is stored: 0 none, 1 the square of relu, 2 gelu in its
   // tanh form, 3 silu.  The same roundings as a product stored and an elementwise kernel run over it.
   int activation;
+  // GATED: how the two halves meet.  gate_kind 0: silu(gate) * up.  1: with g = min(gate, gate_limit) and u = clamp(up, -gate_limit,
+  // gate_limit): g * sigmoid(gate_alpha * g) * (u + gate_shift).
+  int gate_kind;
+  float gate_limit, gate_alpha, gate_shift;
 };
 
 __device__ __forceinline__ float gemv_activate(int kind, float z) {
@@ -179,7 +183,12 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
       // gate and up are rounded to bfloat16 first, as when the product is stored and read back
       const float gate = __bfloat162float(__float2bfloat16_rn(sum));
       const float up = __bfloat162float(__float2bfloat16_rn(second));
-      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+      if (a.gate_kind == 1) {
+        const float g = fminf(gate, a.gate_limit), u = fminf(fmaxf(up, -a.gate_limit), a.gate_limit);
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-a.gate_alpha * g))) * (u + a.gate_shift));
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+      }
     }
   }
   __syncthreads();   // red is written again by the next tile

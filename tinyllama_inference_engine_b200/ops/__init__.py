@@ -310,14 +310,19 @@ class LazyNorm:
         return self._materialize()
 
 
-def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
-    """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves)."""
+def norm_linear(x: "LazyNorm", weight, out, gated: bool = False, clamp=None) -> None:
+    """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves; with ``clamp`` =
+    (limit, alpha, shift) the clamped gate of ``clamped_gate_mul`` instead)."""
     epilogue = "gated" if gated else "store"
     if fast.gemv_fits(out.shape[0], weight.shape[1], norm=True, gated=gated):
         if x.prepared is not None:
-            fast.gemv_fused(x.prepared[0], weight, out, prepared=(x.prepared[1], x.eps), epilogue=epilogue)
+            fast.gemv_fused(x.prepared[0], weight, out, prepared=(x.prepared[1], x.eps), epilogue=epilogue, clamp=clamp)
         else:
-            fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue=epilogue)
+            fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue=epilogue, clamp=clamp)
+    elif clamp is not None:
+        gate_up = torch.empty((out.shape[0], weight.shape[0]), dtype=out.dtype, device=out.device)
+        linear(x.tensor(), weight, gate_up)
+        clamped_gate_mul(gate_up, out, *clamp)
     elif fast.use_skinny and x.prepared is not None and fast.skinny_fits(out.shape[0], weight, x.prepared[0]) and out.is_contiguous():
         # the rows' scale is applied to the product's result: the operand is bfloat16(residual * norm weight) as it was left
         fast.gemm_skinny(x.prepared[0], weight, out, epilogue=epilogue, prepared=(x.prepared[1], x.eps))
@@ -391,10 +396,14 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
         add_(residual, delta)
 
 
-def linear_gated(x, weight, out) -> None:
-    """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel."""
-    if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
-        fast.gemv_fused(x, weight, out, epilogue="gated")
+def linear_gated(x, weight, out, clamp=None) -> None:
+    """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel (``clamp``: see ``norm_linear``)."""
+    if x.dtype == torch.bfloat16 and fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
+        fast.gemv_fused(x, weight, out, epilogue="gated", clamp=clamp)
+    elif clamp is not None:
+        gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        linear(x, weight, gate_up)
+        clamped_gate_mul(gate_up, out, *clamp)
     elif fast.use_tcgen05 and fast.gated_takes(x.shape[0], weight.shape[0], weight.shape[1]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
         fast.gemm_tcgen05_gated(x, weight, out)
     elif fast.use_skinny and fast.skinny_fits(x.shape[0], weight, x) and out.is_contiguous() and out.dtype == torch.bfloat16:

@@ -98,7 +98,7 @@ def prepared_norm_buffers(rows: int, width: int, device) -> tuple:
 GEMV_ACTIVATIONS = {None: 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
 
 
-def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None, activation: str | None = None) -> None:
+def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None, activation: str | None = None, clamp=None) -> None:
     """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
 
     norm      None: ``x`` is bfloat16 [M, K].  (norm_weight, eps, rows): ``x`` is the 32-bit residual stream and
@@ -106,7 +106,8 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
     prepared  (squares, eps): ``x`` is bfloat16(residual * norm weight) [M, K] and ``squares`` [M, tiles] the rows' sums of
               squares, as an earlier "accumulate" with ``prepare`` left them; the operand is the same rmsnorm.
     epilogue  "store": out [M, N] bfloat16 or 32-bit;  "accumulate": out is the 32-bit residual, out += result;
-              "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up.
+              "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up; with ``clamp`` = (limit, alpha, shift) instead
+              g * sigmoid(alpha * g) * (u + shift) for g = min(gate, limit), u = clamp(up, -limit, limit).
     activation ("store" into bfloat16 only) "relu_squared", "gelu_tanh" or "silu": applied to the rounded product before it is stored.
     prepare   ("accumulate" only) (norm_weight [N], x_out bfloat16 [M, N], squares_out [M, ceil(N / 16)]): also store
               bfloat16(out * norm_weight) and the rows' sums of squares per 16 columns, for a later call with ``prepared``.
@@ -151,7 +152,7 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
             raise KernelError("gemv_fused: prepare takes a 32-bit norm weight [N], bfloat16 [M, N] and 32-bit [M, ceil(N / 16)], with accumulate", code="invalid_shape")
         emit = (ops._ptr(norm_weight), ops._ptr(x_out), ops._ptr(squares_out))
     ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, c_int(GEMV_ACTIVATIONS[activation]),
-                                             ops._stream()),
+                                             c_int(0 if clamp is None else 1), *(c_float(float(v)) for v in (clamp or (0.0, 0.0, 0.0))), ops._stream()),
                "gemv_fused")
 
 
@@ -761,10 +762,11 @@ def latent_prefill_library(key_dim: int, value_dim: int):
 
 def latent_prefill_takes(batch, queries, key_dim: int, value_dim: int) -> bool:
     """Whether attention over one cached row per token (values inside the keys) runs on the tensor-core kernel: bfloat16, a prompt
-    portion among the entries, a row width that is a multiple of 16 and a value width that is a multiple of 32, tiles that fit."""
+    portion among the entries, a row width that is a multiple of 16 and a value width that is a multiple of 32 and at most 512 (a warp keeps
+    16 x value width / 2 accumulators in registers), tiles that fit."""
     if not use_latent_prefill or batch is None or batch.max_q_len < LATENT_PREFILL_MIN_ROWS or queries.dtype != torch.bfloat16:
         return False
-    if key_dim % 16 or value_dim % 32 or value_dim > key_dim or batch.num_seqs > 65535 or (64 + 2 * 32) * (key_dim + 8) * 2 > 227 * 1024:
+    if key_dim % 16 or value_dim % 32 or value_dim > key_dim or value_dim > 512 or batch.num_seqs > 65535 or (64 + 2 * 32) * (key_dim + 8) * 2 > 227 * 1024:
         return False
     return latent_prefill_library(key_dim, value_dim).tlie_latent_prefill_fits() == 1
 

@@ -59,7 +59,14 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         act = ws.get("activated", tokens, self.inter, dtype)
-        if self.activation == "clamped_sigmoid":
+        if self.activation == "clamped_sigmoid" and tokens <= ops.fused_rows_limit(dtype, act.device):
+            # few rows: the clamps, the gate and the shift are applied in the stacked product's epilogue
+            clamp = (self.limit, self.alpha, self.shift)
+            if isinstance(x, ops.LazyNorm):
+                ops.norm_linear(x, self.w_gate_up, act, gated=True, clamp=clamp)
+            else:
+                ops.linear_gated(x, self.w_gate_up, act, clamp=clamp)
+        elif self.activation == "clamped_sigmoid":
             # the stacked product, then the clamps, the gate and the shift in one row-wise kernel (32-bit inside)
             gate_up = ws.get("gate_up", tokens, 2 * self.inter, dtype)
             if isinstance(x, ops.LazyNorm):
