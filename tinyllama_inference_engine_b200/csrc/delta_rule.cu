@@ -18,13 +18,17 @@
 //
 // State of a request (32-bit words): for every head the matrix in the order the recurrence reads it,
 // [4 ceil(dim / 32)][vdim][8] (lane l of a column's 8 holds key channels 32 (i / 4) + 4 l + i % 4 at [i][j][l]: four neighbours per
-// 16-byte read of the staged operands), then the convolution's inputs [taps - 1][channels].
+// 16-byte read of the staged operands), then the convolution's inputs [taps - 1][channels].  (TLIE_DELTA_LANES=16 at compile time,
+// and the same number on the host, gives a column 16 lanes and 8 columns to a CTA: twice the warps; measured slower.)
 #include "common.cuh"
 
 namespace tlie {
 
-constexpr int kDeltaLanes = 8;       // lanes that share a column of the state
-constexpr int kDeltaColumns = 16;    // columns per CTA
+#ifndef TLIE_DELTA_LANES
+#define TLIE_DELTA_LANES 8
+#endif
+constexpr int kDeltaLanes = TLIE_DELTA_LANES;        // lanes that share a column of the state (8 or 16; the host lays the state out for the same number)
+constexpr int kDeltaColumns = 128 / kDeltaLanes;     // columns per CTA
 constexpr int kDeltaThreads = kDeltaLanes * kDeltaColumns;
 constexpr int kDeltaMaxTaps = 8;
 
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
   const int kv = head / (heads / kv_heads);
   const int qk = kv_heads * dim;
   const int width = 2 * qk + heads * vdim + heads + heads * dim;
-  const int held = 4 * ((dim + 31) / 32);   // key channels per lane that are stored
+  const int held = 4 * ((dim + 4 * kDeltaLanes - 1) / (4 * kDeltaLanes));   // key channels per lane that are stored
   const size_t matrix = (size_t)held * vdim * kDeltaLanes;
   float* mine = state + (size_t)state_slots[entry] * state_stride + (size_t)head * matrix;
 
@@ -188,9 +192,9 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
       float kk[R];
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 32 + lane * 4);
-        const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 32 + lane * 4);
-        const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 32 + lane * 4);
+        const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 4 * kDeltaLanes + lane * 4);
+        const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 4 * kDeltaLanes + lane * 4);
+        const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 4 * kDeltaLanes + lane * 4);
         const float q[4] = {q4.x, q4.y, q4.z, q4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w}, g[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -283,7 +287,7 @@ TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state
                                 int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   if (entries <= 0) return 0;
   if (dim < 1 || dim > 256 || kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
-  const int r = 4 * ((dim + 31) / 32);
+  const int r = 4 * ((dim + 4 * kDeltaLanes - 1) / (4 * kDeltaLanes));
 #define TLIE_DELTA(R) \
   if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream)
   TLIE_DELTA(4);

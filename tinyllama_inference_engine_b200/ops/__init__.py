@@ -38,7 +38,7 @@ def core():
 def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
     return [build_library("tlie_core", CORE_SOURCES), build_library("tlie_recurrent", RECURRENT_SOURCES),
-            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library("tlie_delta_rule", DELTA_RULE_SOURCES)] + fast.build_all()
+            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library(f"tlie_delta_rule_l{DELTA_LANES}", DELTA_RULE_SOURCES, {"TLIE_DELTA_LANES": DELTA_LANES})] + fast.build_all()
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -502,16 +502,19 @@ def mingru_scan(zxg, bias_z, bias_x, state, seq_starts, state_slots, out, max_ro
                                         _i32(state_slots, "state_slots"), _ptr(out), c_int(entries), c_int(width), c_int(runs), _stream()), "mingru_scan")
 
 
-DELTA_LANES = 8   # lanes that share a column of the delta rule's state: the matrix is stored [4 ceil(dim / 32)][vdim][8] per head
+import os as _os
+
+# lanes that share a column of the delta rule's state (8 or 16): the matrix is stored [4 ceil(dim / (4 lanes))][vdim][lanes] per head
+DELTA_LANES = int(_os.environ.get("TLIE_DELTA_LANES", "8"))
 
 
 def delta_rule_library():
-    return load_library("tlie_delta_rule", DELTA_RULE_SOURCES)
+    return load_library(f"tlie_delta_rule_l{DELTA_LANES}", DELTA_RULE_SOURCES, {"TLIE_DELTA_LANES": DELTA_LANES})
 
 
 def delta_state_words(heads: int, dim: int, vdim: int, channels: int, taps: int) -> tuple[int, int]:
     """(words of a request's delta-rule state, where the convolution's inputs start in it): the heads' matrices, then taps - 1 rows of inputs."""
-    matrices = heads * 4 * (-(-dim // 32)) * DELTA_LANES * vdim
+    matrices = heads * 4 * (-(-dim // (4 * DELTA_LANES))) * DELTA_LANES * vdim
     return matrices + (taps - 1) * channels, matrices
 
 
